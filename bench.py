@@ -1,0 +1,437 @@
+#!/usr/bin/env python
+"""Benchmark of the weight-quantized matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2|cfg4|cfg5]
+
+Default workload (cfg2): the W4A16 g=32 decode sweep -- M in {1, 4, 16} over the SmolLM2-1.7B
+projection shapes (K, N) in {(2048,2048), (2048,8192), (8192,2048), (2048,49152)}.  One step is
+one pass over the 12 (shape, M) calls.  Metric: weight-HBM GB/s = (packed + scale bytes of all
+calls) / device time.  Every call of a step reads its own weight buffer and steps rotate through
+several sets of buffers, so no weight byte is re-read within ~700 MB of traffic (L2 is 126 MB).
+
+With --gpus N > 1 (launched under torchrun, one rank per GPU) each rank holds an N-column shard
+of every linear -- the shard has the cfg2 shape, so per-GPU work is fixed (weak scaling) and the
+global linear is N times wider -- and the outputs are reassembled with an NCCL all-gather inside
+the timed region.
+
+--impl reference times the reference's CPU path (the NumPy dequantise-then-BLAS matvec of
+examples/38_quantized_matmul.py:215-232, restated in oracle/qmm_oracle.py) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG2_SHAPES = [(2048, 2048), (2048, 8192), (8192, 2048), (2048, 49152)]   # (K, N)
+CFG2_MS = [1, 4, 16]
+CFG4_SHAPES = [(4096, 4096), (4096, 14336), (14336, 4096)]
+CFG4_MS = [512, 2048, 8192]
+CFG5_SHAPES = [(8192, 28672), (28672, 8192), (8192, 128256)]
+CFG5_MS = [1, 16, 64]
+GROUP = 32
+
+
+def weight_bytes(k: int, n: int) -> int:
+    return n * k // 2 + n * (k // GROUP) * 2
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------------------------
+# clocks sampling during the timed region
+# --------------------------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------------------
+# reference arm: the reference's CPU path on the host cores
+# --------------------------------------------------------------------------------------------
+def run_reference(args, rank: int, world: int):
+    if rank != 0:
+        return
+    from oracle import qmm_oracle as O
+    rng = np.random.default_rng(0)
+    cases = []
+    for (k, n) in CFG2_SHAPES:
+        wp, s = O.make_w4(rng, n, k, GROUP, np.float16)
+        x = rng.standard_normal((16, k)).astype(np.float16)
+        cases.append((k, n, wp, s, x))
+
+    def sweep(sel):
+        for (k, n, wp, s, x) in sel:
+            for m in CFG2_MS:
+                O.fast_matvec_int4(x[:m], wp, s, GROUP)
+
+    # size the per-step sample from one full untimed sweep so the run ends within minutes
+    t0 = time.perf_counter()
+    sweep(cases)
+    full = time.perf_counter() - t0
+    total_steps = args.steps + args.warmup
+    if full * total_steps <= 150.0:
+        sel, sample = cases, "full cfg2 sweep (12 calls)"
+    else:
+        sel, sample = cases[:3], "cfg2 sweep without the (2048,49152) shape (9 calls)"
+    nbytes = sum(weight_bytes(k, n) for (k, n, *_r) in sel) * len(CFG2_MS)
+    for _ in range(args.warmup):
+        sweep(sel)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        sweep(sel)
+    dt = time.perf_counter() - t0
+    value = nbytes * args.steps / dt / 1e9
+    cores = os.cpu_count()
+    line = {
+        "impl": "reference", "metric": "w4a16_gemv_weight_hbm_gbs", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg2: W4A16 g=32 GEMV sweep, M in {1,4,16} x SmolLM2-1.7B shapes", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": sample + "; NumPy dequantise-to-float32 + BLAS, as examples/38_quantized_matmul.py:215-232"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------
+# our arm
+# --------------------------------------------------------------------------------------------
+class Call:
+    """One (shape, M) quantized-linear call with device-resident operands, bound to the C ABI."""
+
+    def __init__(self, lib, torch, k, n, m, dev, seed, x_dtype="f16"):
+        from locomp_b200 import _lib
+        g = torch.Generator(device=dev).manual_seed(seed)
+        self.k, self.n, self.m = k, n, m
+        self.w = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev, generator=g)
+        self.s = (torch.randn(n, k // GROUP, device=dev, generator=g).abs() * 0.02).to(torch.float16)
+        xdt = torch.float16 if x_dtype == "f16" else torch.bfloat16
+        self.x = torch.randn(m, k, device=dev, generator=g).to(xdt)
+        self.out = torch.empty(m, n, dtype=xdt, device=dev)
+        code = _lib.F16 if x_dtype == "f16" else _lib.BF16
+        self.ws_bytes = lib.lcq_matmul_workspace_bytes(4, m, n, k, GROUP, code, _lib.F16, code, 0)
+        assert self.ws_bytes != (1 << 64) - 1
+        self.args = None
+        self.lib = lib
+        self.code = code
+
+    def bind(self, ws):
+        from locomp_b200 import _lib
+        self.args = (self.x.data_ptr(), self.w.data_ptr(), self.s.data_ptr(), self.out.data_ptr(), self.m, self.n,
+                     self.k, GROUP, self.code, _lib.F16, self.code, 0, ws.data_ptr(), ws.numel())
+
+    def launch(self, stream_ptr):
+        rc = self.lib.lcq_matmul_int4(*self.args, stream_ptr)
+        if rc != 0:
+            raise RuntimeError(f"lcq_matmul_int4 failed: {self.lib.lcq_last_error().decode()}")
+
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch
+    import locomp_b200 as L
+    from locomp_b200 import _lib
+    lib = _lib.lib()
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+
+    if args.workload == "cfg2":
+        shapes, ms, xdt = CFG2_SHAPES, CFG2_MS, "f16"
+    elif args.workload == "cfg4":
+        shapes, ms, xdt = CFG4_SHAPES, CFG4_MS, "bf16"
+    else:
+        shapes, ms, xdt = CFG5_SHAPES, CFG5_MS, "f16"
+
+    # cfg5 is the strong-scaling form: the global N is split across ranks
+    def local_n(n):
+        if args.workload == "cfg5":
+            assert n % world == 0
+            return n // world
+        return n
+
+    per_set_bytes = sum(weight_bytes(k, local_n(n)) for (k, n) in shapes) * len(ms)
+    nsets = max(2, min(8, int(np.ceil(640e6 / per_set_bytes))))
+    sets = []
+    for si in range(nsets):
+        calls = []
+        for ci, (k, n) in enumerate(shapes):
+            for m in ms:
+                calls.append(Call(lib, torch, k, local_n(n), m, dev, seed=1000 * si + 10 * ci + m + rank, x_dtype=xdt))
+        sets.append(calls)
+    ws = torch.zeros(max(max(c.ws_bytes for c in sets[0]), 256), dtype=torch.uint8, device=dev)
+    for calls in sets:
+        for c in calls:
+            c.bind(ws)
+    gathered = None
+    if world > 1:
+        gathered = [torch.empty(world, c.m, c.n, dtype=c.out.dtype, device=dev) for c in sets[0]]
+    torch.cuda.synchronize()
+
+    stream = torch.cuda.Stream(device=dev)
+    sp = stream.cuda_stream
+
+    def step_eager(si):
+        for ci, c in enumerate(sets[si]):
+            c.launch(sp)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[ci], c.out)
+
+    # eager warm-up (also sets kernel attributes before any graph capture)
+    with torch.cuda.stream(stream):
+        for si in range(nsets):
+            step_eager(si)
+    torch.cuda.synchronize()
+    _lib.check(lib.lcq_check_device_status(None))
+
+    graphs = None
+    if world == 1 and not args.no_graph:
+        graphs = []
+        for si in range(nsets):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                cap = torch.cuda.current_stream().cuda_stream
+                for c in sets[si]:
+                    c.launch(cap)
+            graphs.append(g)
+        torch.cuda.synchronize()
+
+    def step(i):
+        si = i % nsets
+        if graphs is not None:
+            graphs[si].replay()
+        else:
+            step_eager(si)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for i in range(args.warmup):
+            step(i)
+        barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(args.steps):
+            step(args.warmup + i)
+        e1.record(stream)
+        barrier()
+        clocks = sampler.stop() if rank == 0 else None
+    ms_total = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    _lib.check(lib.lcq_check_device_status(None))
+
+    total_bytes = per_set_bytes * world * args.steps
+    flops = sum(2.0 * m * local_n(n) * k for (k, n) in shapes for m in ms) * world * args.steps
+    if args.workload == "cfg4":
+        metric, unit, value = "w4a16_prefill_gemm_tflops", "TFLOP/s", flops / (ms_total * 1e-3) / 1e12
+    else:
+        metric, unit, value = "w4a16_gemv_weight_hbm_gbs", "GB/s", total_bytes / (ms_total * 1e-3) / 1e9
+
+    line = {
+        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+        "scaling": "strong" if args.workload == "cfg5" else "weak", "vs_baseline": None,
+        "dtype": "f16" if xdt == "f16" else "bf16", "data": "synthetic",
+        "config": {
+            "workload": {"cfg2": "cfg2: W4A16 g=32 GEMV sweep, M in {1,4,16} x SmolLM2-1.7B shapes (K,N)",
+                         "cfg4": "cfg4: W4A16 g=32 prefill GEMM, M in {512,2048,8192} x Llama-3-8B shapes",
+                         "cfg5": "cfg5: column-sharded W4A16 g=32, 70B shapes, M in {1,16,64}"}[args.workload],
+            "shapes_KN": shapes, "M": ms, "calls_per_step": len(shapes) * len(ms), "group_size": GROUP,
+            "l2_hygiene": f"every call reads its own weights; {nsets} rotating sets of {per_set_bytes / 1e6:.0f} MB",
+            "launch": "cuda_graph" if graphs is not None else "eager",
+            "sharding": None if world == 1 else f"N-column shards + NCCL all-gather, {world} ranks",
+        },
+        "gpu_launches": args.steps * len(shapes) * len(ms),
+        "weight_bytes_per_step": per_set_bytes * world,
+    }
+    if rank == 0:
+        line["clocks"] = clocks
+    # ---------------------------------------------------------------- roofline of the dominant kernel
+    if rank == 0 and args.workload != "cfg4":
+        big = [c for calls in sets for c in calls if c.m == ms[0] and (c.k, c.n) == (shapes[-1][0], local_n(shapes[-1][1]))]
+        durs = []
+        with torch.cuda.stream(stream):
+            for rep in range(6):
+                for c in big:
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(stream)
+                    c.launch(sp)
+                    b.record(stream)
+                    durs.append((a, b))
+                # other sets' small calls between repeats keep the big buffers out of L2
+                for c in sets[rep % nsets]:
+                    if c not in big:
+                        c.launch(sp)
+        torch.cuda.synchronize()
+        times = [a.elapsed_time(b) for (a, b) in durs][len(big):]
+        avg_ms = sum(times) / len(times)
+        k, n = big[0].k, big[0].n
+        achieved = weight_bytes(k, n) / (avg_ms * 1e-3) / 1e9
+        line["roofline"] = {
+            "bound": "hbm", "kernel": f"w4a16_gemv_kernel M={ms[0]} K={k} N={n}", "achieved": achieved,
+            "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
+            "frac": achieved / peaks["hbm_gbs"], "avg_launch_us": avg_ms * 1e3,
+            "algorithmic_bytes_per_launch": weight_bytes(k, n), "traffic": None,
+        }
+    # ---------------------------------------------------------------- end-to-end through the reference-facing call
+    if args.workload == "cfg2":
+        host_sets = []
+        rng = np.random.default_rng(0)
+        h2d = d2h = 0
+        for (k, n) in shapes:
+            wp = torch.from_numpy(rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)).pin_memory()
+            s = torch.from_numpy((np.abs(rng.standard_normal((n, k // GROUP))) * 0.02).astype(np.float16)).pin_memory()
+            x = torch.from_numpy(rng.standard_normal((16, k)).astype(np.float16)).pin_memory()
+            host_sets.append((wp.numpy(), s.numpy(), x.numpy(), (wp, s, x)))
+            for m in ms:
+                h2d += wp.numel() + s.numel() * 2 + m * k * 2
+                d2h += m * n * 2
+        e2e_steps = max(3, min(args.steps, 10))
+
+        def e2e_step():
+            for (wp, s, x, _keep) in host_sets:
+                for m in ms:
+                    L.gpu_matvec_int4(x[:m], wp, s, GROUP)      # host arrays in, host array out
+        e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        if dist is not None:
+            t = torch.tensor([dt], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        line["e2e"] = {"value": per_set_bytes * world * e2e_steps / dt / 1e9, "unit": "GB/s",
+                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                       "call": "locomp_b200.gpu_matvec_int4(x, w_packed, scales, 32) with pinned host arrays: "
+                               "uploads x, weights and scales, runs the kernel, copies the result back -- every call"}
+    # ---------------------------------------------------------------- CPU baseline on the host cores
+    if rank == 0 and world == 1 and args.workload == "cfg2" and not args.no_cpu_baseline:
+        from oracle import qmm_oracle as O
+        rng = np.random.default_rng(0)
+        k, n = 2048, 8192
+        wp, s = O.make_w4(rng, n, k, GROUP, np.float16)
+        x = rng.standard_normal((16, k)).astype(np.float16)
+        reps = 0
+        for _ in range(5):
+            O.fast_matvec_int4(x[:1], wp, s, GROUP)
+        t0 = time.perf_counter()
+        while time.perf_counter() - t0 < 10.0 and reps < 15 * 3:
+            for m in ms:
+                O.fast_matvec_int4(x[:m], wp, s, GROUP)
+            reps += 1
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {
+            "value": weight_bytes(k, n) * len(ms) * reps / dt / 1e9, "unit": "GB/s", "cores": os.cpu_count(),
+            "kind": "port",
+            "sample": f"(K,N)=(2048,8192), M in {{1,4,16}}, {reps} passes; NumPy dequantise-to-float32 + BLAS "
+                      "(oracle.fast_matvec_int4, restating examples/38_quantized_matmul.py:215-232)"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg4", "cfg5"])
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch multi-GPU runs with torch.distributed.run (one rank per GPU)")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

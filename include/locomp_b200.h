@@ -1,0 +1,134 @@
+/*
+ * locomp_b200 -- C ABI of the B200 (sm_100a) weight-quantized matmul / dequantize library.
+ *
+ * The library replaces, for NVIDIA B200, the four operators that the reference project
+ * (Zyora-Dev/locomp v1.0.0) JIT-generates from examples/38_quantized_matmul.py and
+ * examples/52_dequantize.py.  The reference has no fixed C ABI for them: it emits one
+ * `extern "C" void locomp_launch_<kernel>(int,int,int,int,void** args)` per kernel AND per
+ * constexpr tuple (locomp/backends/cuda_codegen.py:349-389), called through ctypes
+ * (locomp/api.py:805-851).  The entry points below are what a fixed binding for the same
+ * operators binds instead; each comment names the reference interface it stands in for.
+ *
+ * Conventions
+ *   - All pointers are DEVICE pointers unless the name says host.  Row-major, contiguous.
+ *   - w_packed : uint8 [N, K/2], low nibble = even k, high nibble = odd k, stored value = q + 8
+ *   - w_int8   : int8  [N, K]
+ *   - scales   : [N, K/group_size], dtype given by scale_dtype
+ *   - x        : [M, K]   (M = 1 is the reference's matvec),  out : [M, N]
+ *   - stream   : a cudaStream_t passed as void* (NULL = legacy default stream).  Calls are
+ *                stream-ordered and never synchronise the device.
+ *   - Every function returns an lcq_status (0 = ok, negative = error) and never throws,
+ *     exits, traps the device or allocates device memory unless its comment says so.
+ */
+#ifndef LOCOMP_B200_H
+#define LOCOMP_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define LCQ_OK               0
+#define LCQ_ERR_BAD_ARG     (-1)  /* null pointer, non-positive size, K % group_size != 0, ...   */
+#define LCQ_ERR_UNSUPPORTED (-2)  /* dtype / shape combination no kernel covers                  */
+#define LCQ_ERR_CUDA        (-3)  /* a CUDA runtime/driver call failed; see lcq_last_error()     */
+#define LCQ_ERR_WORKSPACE   (-4)  /* workspace missing, misaligned or too small                  */
+#define LCQ_ERR_TIMEOUT     (-5)  /* a bounded device-side wait expired (reported by lcq_check_device_status) */
+
+/* dtype codes for x_dtype / scale_dtype / out_dtype */
+#define LCQ_F32  0
+#define LCQ_F16  1
+#define LCQ_BF16 2
+
+/* algorithm selector for lcq_matmul_int4/int8 */
+#define LCQ_ALGO_AUTO    0   /* pick by shape and dtype                                         */
+#define LCQ_ALGO_SIMT    1   /* warp-per-row CUDA-core kernel; any K % group_size == 0           */
+#define LCQ_ALGO_GEMV_TC 2   /* M <= 16: TMA-staged int4 stream + warp-level MMA, split-K        */
+#define LCQ_ALGO_GEMM_TC 3   /* M >= 17: TMA + in-kernel dequant + tcgen05 MMA, TMEM accumulators */
+
+int         lcq_version(void);
+const char* lcq_status_string(int status);
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* lcq_last_error(void);
+
+/* Name, SM count and L2 size of a device; any out pointer may be NULL. */
+int lcq_device_info(int device, char* name, size_t name_len, int* sm_count, int* l2_bytes,
+                    int* cc_major, int* cc_minor);
+
+/*
+ * Dequantize int4 -> float.  out[r, k] = (float(nibble) - 8) * float(scales[r, k / group_size]),
+ * one rounding in float32; out_dtype F16/BF16 round that float32 value to nearest-even.
+ * Replaces the generated kernel `dequant_int4` (examples/52_dequantize.py:27-53), i.e.
+ * locomp_launch_dequant_int4(grid,..., args = {W, SCALES, OUT}) with K, HALF_K, NUM_SCALES and
+ * GROUP_SIZE baked in.  Requires K % 2 == 0 and K % group_size == 0 (the reference kernel
+ * silently truncates K to a multiple of 256; this one covers all of K).
+ */
+int lcq_dequant_int4(const void* w_packed, const void* scales, void* out,
+                     int64_t N, int64_t K, int group_size,
+                     int scale_dtype, int out_dtype, void* stream);
+
+/* Dequantize int8 -> float: out[r, k] = float(w[r, k]) * scales[r, k / group_size].
+ * Replaces `dequant_int8` (examples/52_dequantize.py:60-74). */
+int lcq_dequant_int8(const void* w_int8, const void* scales, void* out,
+                     int64_t N, int64_t K, int group_size,
+                     int scale_dtype, int out_dtype, void* stream);
+
+/*
+ * Quantized matmul, int4 weights: out[m, n] = sum_k x[m, k] * (nibble(n, k) - 8) * scales[n, k / G],
+ * float32 accumulation, out rounded to out_dtype.  M = 1 with F32 everywhere is the reference's
+ * `dequant_matvec_int4` (examples/38_quantized_matmul.py:30-87; launch wrapper
+ * locomp_launch_dequant_matvec_int4, args = {X, W, scales, O}); M > 1 and 16-bit dtypes are the
+ * batched generalisation X @ dequant(W)^T.  The reference kernel asserts K % 256 == 0
+ * (examples/38_quantized_matmul.py:145); this one needs only K % group_size == 0, K % 2 == 0.
+ *
+ * workspace: device scratch of at least lcq_matmul_workspace_bytes(...) bytes, 256-byte aligned,
+ * ZERO-FILLED before its first use; the kernels leave it zeroed again, so one buffer can be
+ * reused by consecutive calls on one stream.  Calls that may overlap on the GPU need separate
+ * workspaces.  May be NULL when the size query returns 0.
+ */
+int lcq_matmul_int4(const void* x, const void* w_packed, const void* scales, void* out,
+                    int M, int N, int K, int group_size,
+                    int x_dtype, int scale_dtype, int out_dtype, int algo,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* Quantized matmul, int8 weights; M = 1 / F32 is `dequant_matvec_int8`
+ * (examples/38_quantized_matmul.py:94-134).  Per-output-channel scales are group_size = K. */
+int lcq_matmul_int8(const void* x, const void* w_int8, const void* scales, void* out,
+                    int M, int N, int K, int group_size,
+                    int x_dtype, int scale_dtype, int out_dtype, int algo,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* Bytes of workspace lcq_matmul_int4 / lcq_matmul_int8 need for this problem on the current
+ * device (0 if none).  wbits is 4 or 8.  Returns (size_t)-1 for an invalid problem. */
+size_t lcq_matmul_workspace_bytes(int wbits, int M, int N, int K, int group_size,
+                                  int x_dtype, int scale_dtype, int out_dtype, int algo);
+
+/* Which algorithm LCQ_ALGO_AUTO resolves to for this problem (one of LCQ_ALGO_*), or a
+ * negative status. */
+int lcq_matmul_select_algo(int wbits, int M, int N, int K, int group_size,
+                           int x_dtype, int scale_dtype, int out_dtype);
+
+/*
+ * Device-side status word.  Kernels that wait on an mbarrier do so with an iteration limit;
+ * when a wait gives up the kernel records it here and returns instead of hanging.  Reads the
+ * word of the current device (synchronising `stream` first), clears it and returns LCQ_OK or
+ * LCQ_ERR_TIMEOUT.  No counterpart in the reference, whose launch wrapper never checks errors.
+ */
+int lcq_check_device_status(void* stream);
+
+/*
+ * Diagnostic, host only: builds the work plan the GEMV_TC kernel would use for (M, N, K) on a
+ * device with sm_count SMs and replays its device-side schedule on the CPU, checking that
+ * every (row block, k tile) is produced exactly once and that scratch slots and contributor
+ * counts agree.  fields (may be NULL) receives {grid, row blocks, k ranges, tiles per range,
+ * CTAs per range, max split, shared-memory bytes, m tiles}.  No counterpart in the reference.
+ */
+int lcq_gemv_tc_plan_check(int M, int N, int K, int sm_count, int* fields);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LOCOMP_B200_H */

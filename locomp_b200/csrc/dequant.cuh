@@ -1,0 +1,178 @@
+// Streaming dequantize kernels: packed int4 / int8 weights -> f32 / f16 / bf16.
+//
+// Reference behaviour: examples/52_dequantize.py:27-53 (int4) and :60-74 (int8):
+//   out[r, 2j]   = (float(b & 15) - 8) * scales[r, 2j / G]
+//   out[r, 2j+1] = (float(b >> 4) - 8) * scales[r, (2j+1) / G]
+// Because K % G == 0, the scale of flat element e = r*K + k is scales_flat[e / G], so the
+// fast paths index everything flat and never need the row.
+//
+// HBM-bound (write dominated: 4 B out per 0.5 B in for f32).  The fast int4 path reads one
+// 32-bit word per lane (128 B per warp, coalesced), redistributes nibbles with two warp
+// shuffles so that every store instruction writes 32 x 16 B = 512 contiguous bytes.
+#pragma once
+#include "common.cuh"
+
+namespace lcq {
+
+template <typename OT> struct Out4;   // 4 consecutive outputs, one vector store
+template <> struct Out4<float> {
+  static __device__ __forceinline__ void store(float* p, float a, float b, float c, float d) {
+    __stcs(reinterpret_cast<float4*>(p), make_float4(a, b, c, d));
+  }
+};
+template <> struct Out4<__half> {
+  static __device__ __forceinline__ void store(__half* p, float a, float b, float c, float d) {
+    __half2 lo = __floats2half2_rn(a, b), hi = __floats2half2_rn(c, d);
+    uint2 v = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    __stcs(reinterpret_cast<uint2*>(p), v);
+  }
+};
+template <> struct Out4<__nv_bfloat16> {
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    __stcs(reinterpret_cast<uint2*>(p), v);
+  }
+};
+
+// ---- int4 fast path: K % 8 == 0, G % 8 == 0, w 4-byte aligned, out 16-byte aligned (f32).
+// total_words = N*K/8.  Each warp iteration covers 32 words = 256 weights.
+template <typename ST, typename OT>
+__global__ void __launch_bounds__(256) dequant_w4_words_kernel(const uint32_t* __restrict__ w,
+                                                               const ST* __restrict__ scales,
+                                                               OT* __restrict__ out,
+                                                               long long total_words, int G) {
+  const int lane = threadIdx.x & 31;
+  const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long n_warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long n_iters = (total_words + 31) >> 5;
+  for (long long it = warp_id; it < n_iters; it += n_warps) {
+    const long long wb = it << 5;
+    const long long wi = wb + lane;
+    const uint32_t word = (wi < total_words) ? __ldg(w + wi) : 0u;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      // lane l of store j writes weights [8*(wb+16j) + 4l, +4) = half (l&1) of word wb+16j+l/2
+      const uint32_t wj = __shfl_sync(0xffffffffu, word, 16 * j + (lane >> 1));
+      const long long src_word = wb + 16 * j + (lane >> 1);
+      if (src_word < total_words) {
+        const uint32_t nib = (wj >> (16 * (lane & 1))) & 0xFFFFu;
+        const long long e0 = src_word * 8 + 4 * (lane & 1);
+        const float sc = to_f32<ST>(__ldg(scales + e0 / G));
+        const float f0 = (small_uint_to_f32(nib & 15u) - 8.0f) * sc;
+        const float f1 = (small_uint_to_f32((nib >> 4) & 15u) - 8.0f) * sc;
+        const float f2 = (small_uint_to_f32((nib >> 8) & 15u) - 8.0f) * sc;
+        const float f3 = (small_uint_to_f32((nib >> 12) & 15u) - 8.0f) * sc;
+        Out4<OT>::store(out + e0, f0, f1, f2, f3);
+      }
+    }
+  }
+}
+
+// ---- int4 generic path: one thread per packed byte; any even K, any G dividing K.
+template <typename ST, typename OT>
+__global__ void __launch_bounds__(256) dequant_w4_bytes_kernel(const uint8_t* __restrict__ w,
+                                                               const ST* __restrict__ scales,
+                                                               OT* __restrict__ out,
+                                                               long long total_bytes, int K, int G) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const int half_k = K >> 1, ns = K / G;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_bytes; i += stride) {
+    const long long r = i / half_k;
+    const int j = static_cast<int>(i - r * half_k);
+    const uint32_t b = __ldg(w + i);
+    const int k0 = 2 * j, k1 = 2 * j + 1;
+    const float s0 = to_f32<ST>(__ldg(scales + r * ns + k0 / G));
+    const float s1 = to_f32<ST>(__ldg(scales + r * ns + k1 / G));
+    out[r * K + k0] = from_f32<OT>((small_uint_to_f32(b & 15u) - 8.0f) * s0);
+    out[r * K + k1] = from_f32<OT>((small_uint_to_f32(b >> 4) - 8.0f) * s1);
+  }
+}
+
+// float(int8) for the 4 bytes of a word without conversion instructions.
+__device__ __forceinline__ void int8x4_to_f32(uint32_t v, float (&f)[4]) {
+  v ^= 0x80808080u;  // bias to unsigned: b + 128
+  f[0] = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7540)) - 8388736.0f;
+  f[1] = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7541)) - 8388736.0f;
+  f[2] = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7542)) - 8388736.0f;
+  f[3] = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7543)) - 8388736.0f;
+}
+
+// ---- int8 fast path: K % 4 == 0, G % 4 == 0; one 32-bit word (4 weights) per thread.
+template <typename ST, typename OT>
+__global__ void __launch_bounds__(256) dequant_w8_words_kernel(const uint32_t* __restrict__ w,
+                                                               const ST* __restrict__ scales,
+                                                               OT* __restrict__ out,
+                                                               long long total_words, int G) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_words; i += stride) {
+    float f[4];
+    int8x4_to_f32(__ldg(w + i), f);
+    const float sc = to_f32<ST>(__ldg(scales + (i * 4) / G));
+    Out4<OT>::store(out + i * 4, f[0] * sc, f[1] * sc, f[2] * sc, f[3] * sc);
+  }
+}
+
+// ---- int8 generic path: one thread per weight.
+template <typename ST, typename OT>
+__global__ void __launch_bounds__(256) dequant_w8_elems_kernel(const int8_t* __restrict__ w,
+                                                               const ST* __restrict__ scales,
+                                                               OT* __restrict__ out,
+                                                               long long total, int K, int G) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const int ns = K / G;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long r = i / K;
+    const int k = static_cast<int>(i - r * K);
+    const float sc = to_f32<ST>(__ldg(scales + r * ns + k / G));
+    out[i] = from_f32<OT>(static_cast<float>(__ldg(w + i)) * sc);
+  }
+}
+
+inline int grid_for(long long work_items, int per_block, int sm_count, int blocks_per_sm) {
+  long long need = (work_items + per_block - 1) / per_block;
+  long long cap = static_cast<long long>(sm_count) * blocks_per_sm;
+  if (need < 1) need = 1;
+  return static_cast<int>(need < cap ? need : cap);
+}
+
+template <typename ST, typename OT>
+int launch_dequant(int wbits, const void* w, const void* scales, void* out, long long N, long long K, int G,
+                   int sm_count, cudaStream_t stream) {
+  const long long total = N * K;
+  if (total == 0) return LCQ_OK;
+  const size_t out_vec_align = 4 * sizeof(OT);
+  if (wbits == 4) {
+    const bool fast = (K % 8 == 0) && (G % 8 == 0) && aligned(w, 4) && aligned(out, out_vec_align);
+    if (fast) {
+      const long long words = total / 8;
+      // 8 warps per block, 4 iterations per warp at full grid
+      const int grid = grid_for((words + 31) / 32, 8, sm_count, 16);
+      dequant_w4_words_kernel<ST, OT><<<grid, 256, 0, stream>>>(
+          static_cast<const uint32_t*>(w), static_cast<const ST*>(scales), static_cast<OT*>(out), words, G);
+    } else {
+      const long long bytes = total / 2;
+      const int grid = grid_for(bytes, 256, sm_count, 16);
+      dequant_w4_bytes_kernel<ST, OT><<<grid, 256, 0, stream>>>(
+          static_cast<const uint8_t*>(w), static_cast<const ST*>(scales), static_cast<OT*>(out), bytes,
+          static_cast<int>(K), G);
+    }
+  } else {
+    const bool fast = (K % 4 == 0) && (G % 4 == 0) && aligned(w, 4) && aligned(out, out_vec_align);
+    if (fast) {
+      const long long words = total / 4;
+      const int grid = grid_for(words, 256, sm_count, 16);
+      dequant_w8_words_kernel<ST, OT><<<grid, 256, 0, stream>>>(
+          static_cast<const uint32_t*>(w), static_cast<const ST*>(scales), static_cast<OT*>(out), words, G);
+    } else {
+      const int grid = grid_for(total, 256, sm_count, 16);
+      dequant_w8_elems_kernel<ST, OT><<<grid, 256, 0, stream>>>(
+          static_cast<const int8_t*>(w), static_cast<const ST*>(scales), static_cast<OT*>(out), total,
+          static_cast<int>(K), G);
+    }
+  }
+  LCQ_CUDA_TRY(cudaGetLastError());
+  return LCQ_OK;
+}
+
+}  // namespace lcq

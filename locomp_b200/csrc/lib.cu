@@ -1,0 +1,394 @@
+// locomp_b200 shared library: the extern "C" boundary declared in include/locomp_b200.h.
+// Single translation unit (the kernel headers are included here) so the device status word
+// and the kernels link without relocatable device code.
+#include <stdarg.h>
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+#include "dequant.cuh"
+#include "gemv_simt.cuh"
+#include "gemv_tc.cuh"
+#include "gemm_tc.cuh"
+
+namespace lcq {
+
+static thread_local char t_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(t_error, sizeof(t_error), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  set_error("CUDA error %d (%s) in %s", static_cast<int>(e), cudaGetErrorString(e), what);
+  return LCQ_ERR_CUDA;
+}
+
+// ---------------------------------------------------------------- tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+int encode_tmap_2d(void* out_map, int dtype_code, const void* base, uint64_t inner, uint64_t outer,
+                   uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, int swizzle_code) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return LCQ_ERR_CUDA;
+  }
+  CUtensorMapDataType dt = dtype_code == 0 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                          : dtype_code == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                            : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMapSwizzle sw = swizzle_code == 0 ? CU_TENSOR_MAP_SWIZZLE_NONE
+                         : swizzle_code == 1 ? CU_TENSOR_MAP_SWIZZLE_32B
+                         : swizzle_code == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                             : CU_TENSOR_MAP_SWIZZLE_128B;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(static_cast<CUtensorMap*>(out_map), dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (inner=%llu outer=%llu stride=%llu box=%ux%u)",
+              static_cast<int>(r), static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
+              static_cast<unsigned long long>(row_stride_bytes), box_inner, box_outer);
+    return LCQ_ERR_CUDA;
+  }
+  return LCQ_OK;
+}
+
+// ---------------------------------------------------------------- device properties (cached per device)
+struct DevInfo { int sm_count = 0; int l2 = 0; int major = 0; int minor = 0; bool ok = false; };
+static DevInfo g_dev[64];
+static std::mutex g_dev_mu;
+
+static int current_dev_info(DevInfo& out) {
+  int dev = 0;
+  LCQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) { set_error("device index %d out of range", dev); return LCQ_ERR_BAD_ARG; }
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  if (!g_dev[dev].ok) {
+    LCQ_CUDA_TRY(cudaDeviceGetAttribute(&g_dev[dev].sm_count, cudaDevAttrMultiProcessorCount, dev));
+    LCQ_CUDA_TRY(cudaDeviceGetAttribute(&g_dev[dev].l2, cudaDevAttrL2CacheSize, dev));
+    LCQ_CUDA_TRY(cudaDeviceGetAttribute(&g_dev[dev].major, cudaDevAttrComputeCapabilityMajor, dev));
+    LCQ_CUDA_TRY(cudaDeviceGetAttribute(&g_dev[dev].minor, cudaDevAttrComputeCapabilityMinor, dev));
+    g_dev[dev].ok = true;
+  }
+  out = g_dev[dev];
+  return LCQ_OK;
+}
+
+static bool dtype_ok(int d) { return d == LCQ_F32 || d == LCQ_F16 || d == LCQ_BF16; }
+
+static int check_problem(int wbits, long long M, long long N, long long K, int G) {
+  if (wbits != 4 && wbits != 8) { set_error("wbits must be 4 or 8, got %d", wbits); return LCQ_ERR_BAD_ARG; }
+  if (M < 0 || N < 0 || K <= 0 || G <= 0) {
+    set_error("bad sizes M=%lld N=%lld K=%lld group_size=%d", M, N, K, G);
+    return LCQ_ERR_BAD_ARG;
+  }
+  if (K % G != 0) { set_error("K=%lld is not a multiple of group_size=%d", K, G); return LCQ_ERR_BAD_ARG; }
+  if (wbits == 4 && (K % 2) != 0) { set_error("int4 weights need an even K, got %lld", K); return LCQ_ERR_BAD_ARG; }
+  if (M > 2000000000LL / 4 || N > 2000000000LL || K > 2000000000LL) {
+    set_error("sizes beyond 32-bit indexing are not supported");
+    return LCQ_ERR_UNSUPPORTED;
+  }
+  return LCQ_OK;
+}
+
+// ---------------------------------------------------------------- dispatch helpers
+template <typename ST>
+static int dequant_by_out(int wbits, const void* w, const void* s, void* out, long long N, long long K, int G,
+                          int out_dtype, int sm, cudaStream_t st) {
+  switch (out_dtype) {
+    case LCQ_F32: return launch_dequant<ST, float>(wbits, w, s, out, N, K, G, sm, st);
+    case LCQ_F16: return launch_dequant<ST, __half>(wbits, w, s, out, N, K, G, sm, st);
+    case LCQ_BF16: return launch_dequant<ST, __nv_bfloat16>(wbits, w, s, out, N, K, G, sm, st);
+  }
+  return LCQ_ERR_BAD_ARG;
+}
+
+static int dequant_entry(int wbits, const void* w, const void* s, void* out, int64_t N, int64_t K, int G,
+                         int scale_dtype, int out_dtype, void* stream) {
+  int rc = check_problem(wbits, 1, N, K, G);
+  if (rc != LCQ_OK) return rc;
+  if (!dtype_ok(scale_dtype) || !dtype_ok(out_dtype)) { set_error("bad dtype code"); return LCQ_ERR_BAD_ARG; }
+  if (N == 0) return LCQ_OK;
+  if (!w || !s || !out) { set_error("null pointer argument"); return LCQ_ERR_BAD_ARG; }
+  DevInfo di;
+  rc = current_dev_info(di);
+  if (rc != LCQ_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (scale_dtype) {
+    case LCQ_F32: return dequant_by_out<float>(wbits, w, s, out, N, K, G, out_dtype, di.sm_count, st);
+    case LCQ_F16: return dequant_by_out<__half>(wbits, w, s, out, N, K, G, out_dtype, di.sm_count, st);
+    case LCQ_BF16: return dequant_by_out<__nv_bfloat16>(wbits, w, s, out, N, K, G, out_dtype, di.sm_count, st);
+  }
+  return LCQ_ERR_BAD_ARG;
+}
+
+template <int WBITS, typename XT, typename ST>
+static int simt_by_out(const void* x, const void* w, const void* s, void* out, int M, int N, int K, int G,
+                       int out_dtype, cudaStream_t st) {
+  switch (out_dtype) {
+    case LCQ_F32: return launch_gemv_simt<WBITS, XT, ST, float>(x, w, s, out, M, N, K, G, st);
+    case LCQ_F16: return launch_gemv_simt<WBITS, XT, ST, __half>(x, w, s, out, M, N, K, G, st);
+    case LCQ_BF16: return launch_gemv_simt<WBITS, XT, ST, __nv_bfloat16>(x, w, s, out, M, N, K, G, st);
+  }
+  return LCQ_ERR_BAD_ARG;
+}
+template <int WBITS, typename XT>
+static int simt_by_scale(const void* x, const void* w, const void* s, void* out, int M, int N, int K, int G,
+                         int scale_dtype, int out_dtype, cudaStream_t st) {
+  switch (scale_dtype) {
+    case LCQ_F32: return simt_by_out<WBITS, XT, float>(x, w, s, out, M, N, K, G, out_dtype, st);
+    case LCQ_F16: return simt_by_out<WBITS, XT, __half>(x, w, s, out, M, N, K, G, out_dtype, st);
+    case LCQ_BF16: return simt_by_out<WBITS, XT, __nv_bfloat16>(x, w, s, out, M, N, K, G, out_dtype, st);
+  }
+  return LCQ_ERR_BAD_ARG;
+}
+template <int WBITS>
+static int simt_entry(const void* x, const void* w, const void* s, void* out, int M, int N, int K, int G,
+                      int x_dtype, int scale_dtype, int out_dtype, cudaStream_t st) {
+  if (M > 4 * 65535) { set_error("SIMT path supports M <= 262140"); return LCQ_ERR_UNSUPPORTED; }
+  switch (x_dtype) {
+    case LCQ_F32: return simt_by_scale<WBITS, float>(x, w, s, out, M, N, K, G, scale_dtype, out_dtype, st);
+    case LCQ_F16: return simt_by_scale<WBITS, __half>(x, w, s, out, M, N, K, G, scale_dtype, out_dtype, st);
+    case LCQ_BF16: return simt_by_scale<WBITS, __nv_bfloat16>(x, w, s, out, M, N, K, G, scale_dtype, out_dtype, st);
+  }
+  return LCQ_ERR_BAD_ARG;
+}
+
+static int select_algo(int wbits, int M, int N, int K, int G, int x_dtype, int scale_dtype, int out_dtype) {
+  (void)out_dtype;
+  if (wbits == 4 && M > 16 && gemm_tc::supported(M, N, K, G, x_dtype, scale_dtype)) return LCQ_ALGO_GEMM_TC;
+  if (wbits == 4 && gemv_tc::supported(M < 16 ? M : 16, N, K, G, x_dtype, scale_dtype)) return LCQ_ALGO_GEMV_TC;
+  return LCQ_ALGO_SIMT;
+}
+
+static int matmul_entry(int wbits, const void* x, const void* w, const void* s, void* out, int M, int N, int K,
+                        int G, int x_dtype, int scale_dtype, int out_dtype, int algo, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+  int rc = check_problem(wbits, M, N, K, G);
+  if (rc != LCQ_OK) return rc;
+  if (!dtype_ok(x_dtype) || !dtype_ok(scale_dtype) || !dtype_ok(out_dtype)) {
+    set_error("bad dtype code");
+    return LCQ_ERR_BAD_ARG;
+  }
+  if (M == 0 || N == 0) return LCQ_OK;
+  if (!x || !w || !s || !out) { set_error("null pointer argument"); return LCQ_ERR_BAD_ARG; }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (algo == LCQ_ALGO_AUTO) algo = select_algo(wbits, M, N, K, G, x_dtype, scale_dtype, out_dtype);
+  DevInfo di;
+  rc = current_dev_info(di);
+  if (rc != LCQ_OK) return rc;
+  if (algo != LCQ_ALGO_SIMT && (di.major != 10)) {
+    set_error("tensor-core kernels are built for sm_100a only; device is sm_%d%d", di.major, di.minor);
+    return LCQ_ERR_UNSUPPORTED;
+  }
+  switch (algo) {
+    case LCQ_ALGO_SIMT:
+      return wbits == 4 ? simt_entry<4>(x, w, s, out, M, N, K, G, x_dtype, scale_dtype, out_dtype, st)
+                        : simt_entry<8>(x, w, s, out, M, N, K, G, x_dtype, scale_dtype, out_dtype, st);
+    case LCQ_ALGO_GEMV_TC: {
+      if (wbits != 4 || !gemv_tc::supported(M < 16 ? M : 16, N, K, G, x_dtype, scale_dtype)) {
+        set_error("GEMV_TC needs int4, group_size 32, K %% 256 == 0, f16 scales, f16/bf16 x");
+        return LCQ_ERR_UNSUPPORTED;
+      }
+      // M > 16: rows of x in chunks of 16 (each chunk re-streams the weights)
+      const size_t xe = 2, oe = out_dtype == LCQ_F32 ? 4 : 2;
+      for (int m0 = 0; m0 < M; m0 += 16) {
+        const int mc = M - m0 < 16 ? M - m0 : 16;
+        rc = gemv_tc::launch(static_cast<const uint8_t*>(x) + static_cast<size_t>(m0) * K * xe, w, s,
+                             static_cast<uint8_t*>(out) + static_cast<size_t>(m0) * N * oe, mc, N, K, x_dtype,
+                             out_dtype, workspace, workspace_bytes, di.sm_count, st);
+        if (rc != LCQ_OK) return rc;
+      }
+      return LCQ_OK;
+    }
+    case LCQ_ALGO_GEMM_TC:
+      if (wbits != 4 || !gemm_tc::supported(M, N, K, G, x_dtype, scale_dtype)) {
+        set_error("GEMM_TC needs int4, group_size 32, K %% 64 == 0, f16 scales, f16/bf16 x");
+        return LCQ_ERR_UNSUPPORTED;
+      }
+      return gemm_tc::launch(x, w, s, out, M, N, K, x_dtype, out_dtype, workspace, workspace_bytes, di.sm_count, st);
+    default:
+      set_error("unknown algo %d", algo);
+      return LCQ_ERR_BAD_ARG;
+  }
+}
+
+}  // namespace lcq
+
+// =================================================================== extern "C"
+using namespace lcq;
+
+extern "C" {
+
+int lcq_version(void) { return 100; }
+
+const char* lcq_status_string(int status) {
+  switch (status) {
+    case LCQ_OK: return "ok";
+    case LCQ_ERR_BAD_ARG: return "bad argument";
+    case LCQ_ERR_UNSUPPORTED: return "unsupported dtype/shape";
+    case LCQ_ERR_CUDA: return "CUDA error";
+    case LCQ_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case LCQ_ERR_TIMEOUT: return "device-side wait timed out";
+    default: return "unknown status";
+  }
+}
+
+const char* lcq_last_error(void) { return t_error; }
+
+int lcq_device_info(int device, char* name, size_t name_len, int* sm_count, int* l2_bytes, int* cc_major,
+                    int* cc_minor) {
+  cudaDeviceProp prop;
+  LCQ_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+  if (name && name_len) { strncpy(name, prop.name, name_len - 1); name[name_len - 1] = 0; }
+  if (sm_count) *sm_count = prop.multiProcessorCount;
+  if (l2_bytes) *l2_bytes = prop.l2CacheSize;
+  if (cc_major) *cc_major = prop.major;
+  if (cc_minor) *cc_minor = prop.minor;
+  return LCQ_OK;
+}
+
+int lcq_dequant_int4(const void* w_packed, const void* scales, void* out, int64_t N, int64_t K, int group_size,
+                     int scale_dtype, int out_dtype, void* stream) {
+  return dequant_entry(4, w_packed, scales, out, N, K, group_size, scale_dtype, out_dtype, stream);
+}
+
+int lcq_dequant_int8(const void* w_int8, const void* scales, void* out, int64_t N, int64_t K, int group_size,
+                     int scale_dtype, int out_dtype, void* stream) {
+  return dequant_entry(8, w_int8, scales, out, N, K, group_size, scale_dtype, out_dtype, stream);
+}
+
+int lcq_matmul_int4(const void* x, const void* w_packed, const void* scales, void* out, int M, int N, int K,
+                    int group_size, int x_dtype, int scale_dtype, int out_dtype, int algo, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+  return matmul_entry(4, x, w_packed, scales, out, M, N, K, group_size, x_dtype, scale_dtype, out_dtype, algo,
+                      workspace, workspace_bytes, stream);
+}
+
+int lcq_matmul_int8(const void* x, const void* w_int8, const void* scales, void* out, int M, int N, int K,
+                    int group_size, int x_dtype, int scale_dtype, int out_dtype, int algo, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+  return matmul_entry(8, x, w_int8, scales, out, M, N, K, group_size, x_dtype, scale_dtype, out_dtype, algo,
+                      workspace, workspace_bytes, stream);
+}
+
+int lcq_matmul_select_algo(int wbits, int M, int N, int K, int group_size, int x_dtype, int scale_dtype,
+                           int out_dtype) {
+  int rc = check_problem(wbits, M, N, K, group_size);
+  if (rc != LCQ_OK) return rc;
+  return select_algo(wbits, M, N, K, group_size, x_dtype, scale_dtype, out_dtype);
+}
+
+size_t lcq_matmul_workspace_bytes(int wbits, int M, int N, int K, int group_size, int x_dtype, int scale_dtype,
+                                  int out_dtype, int algo) {
+  if (check_problem(wbits, M, N, K, group_size) != LCQ_OK) return static_cast<size_t>(-1);
+  if (M == 0 || N == 0) return 0;
+  if (algo == LCQ_ALGO_AUTO) algo = select_algo(wbits, M, N, K, group_size, x_dtype, scale_dtype, out_dtype);
+  if (algo == LCQ_ALGO_SIMT) return 0;
+  int sm = 148;  // B200; refined from the device when one is present
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) sm = v;
+  } else {
+    (void)cudaGetLastError();
+  }
+  if (algo == LCQ_ALGO_GEMV_TC) {
+    if (wbits != 4 || !gemv_tc::supported(M < 16 ? M : 16, N, K, group_size, x_dtype, scale_dtype))
+      return static_cast<size_t>(-1);
+    return gemv_tc::make_plan(M < 16 ? M : 16, N, K, sm).workspace_bytes;
+  }
+  if (algo == LCQ_ALGO_GEMM_TC) {
+    if (wbits != 4 || !gemm_tc::supported(M, N, K, group_size, x_dtype, scale_dtype)) return static_cast<size_t>(-1);
+    return gemm_tc::workspace_bytes(M, N, K);
+  }
+  return static_cast<size_t>(-1);
+}
+
+int lcq_gemv_tc_plan_check(int M, int N, int K, int sm_count, int* fields) {
+  if (!gemv_tc::supported(M, N, K, 32, LCQ_F16, LCQ_F16) || sm_count < 1) {
+    set_error("plan check: problem not covered by GEMV_TC");
+    return LCQ_ERR_UNSUPPORTED;
+  }
+  const gemv_tc::Plan pl = gemv_tc::make_plan(M, N, K, sm_count);
+  const gemv_tc::Params& p = pl.p;
+  if (fields) {
+    fields[0] = pl.grid; fields[1] = p.n_rb; fields[2] = p.n_kr; fields[3] = p.S; fields[4] = p.ctas_per_kr;
+    fields[5] = p.max_split; fields[6] = static_cast<int>(pl.smem_bytes); fields[7] = pl.MT;
+  }
+  if (pl.smem_bytes > 227 * 1024) { set_error("plan check: %zu bytes of shared memory", pl.smem_bytes); return LCQ_ERR_UNSUPPORTED; }
+  // Replay the device-side schedule on the host: every (row block, k tile) exactly once,
+  // slots within bounds and unique, contributor counts consistent.
+  std::vector<int> seen(static_cast<size_t>(p.n_rb) * p.nst, 0);
+  std::vector<int> contrib(p.n_rb, 0);
+  std::vector<int> slot_used(static_cast<size_t>(p.n_rb) * p.n_kr * p.max_split, 0);
+  for (int b = 0; b < pl.grid; ++b) {
+    const int kr = b % p.n_kr, j = b / p.n_kr;
+    const gemv_tc::Sched s = gemv_tc::make_sched(p, kr);
+    if (j >= s.G) continue;
+    const long long t0 = gemv_tc::tile_begin(s, j), t1 = gemv_tc::tile_begin(s, j + 1);
+    if (t1 <= t0) { set_error("plan check: CTA %d has no tiles", b); return LCQ_ERR_BAD_ARG; }
+    int last_rb = -1;
+    for (long long t = t0; t < t1; ++t) {
+      const int rb = static_cast<int>(t / s.S_kr), ks = static_cast<int>(t % s.S_kr);
+      const int kt = kr * p.S + ks;
+      if (rb >= p.n_rb || kt >= p.nst) { set_error("plan check: tile out of range"); return LCQ_ERR_BAD_ARG; }
+      seen[static_cast<size_t>(rb) * p.nst + kt]++;
+      if (rb != last_rb) {
+        int j0, j1;
+        gemv_tc::cover(s, rb, j0, j1);
+        if (j < j0 || j > j1) { set_error("plan check: CTA outside cover"); return LCQ_ERR_BAD_ARG; }
+        const int slot = kr * p.max_split + (j - j0);
+        if (j - j0 >= p.max_split) { set_error("plan check: slot %d >= max_split %d", j - j0, p.max_split); return LCQ_ERR_BAD_ARG; }
+        if (slot_used[(static_cast<size_t>(rb) * p.n_kr * p.max_split) + slot]++) { set_error("plan check: slot reused"); return LCQ_ERR_BAD_ARG; }
+        contrib[rb]++;
+        last_rb = rb;
+      }
+    }
+  }
+  for (size_t i = 0; i < seen.size(); ++i)
+    if (seen[i] != 1) { set_error("plan check: tile %zu covered %d times", i, seen[i]); return LCQ_ERR_BAD_ARG; }
+  for (int rb = 0; rb < p.n_rb; ++rb)
+    if (contrib[rb] != gemv_tc::contributors(p, rb)) {
+      set_error("plan check: row block %d has %d contributors, kernel expects %d", rb, contrib[rb], gemv_tc::contributors(p, rb));
+      return LCQ_ERR_BAD_ARG;
+    }
+  return LCQ_OK;
+}
+
+int lcq_check_device_status(void* stream) {
+  LCQ_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  int v = 0;
+  LCQ_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)));
+  if (v != 0) {
+    const int zero = 0;
+    LCQ_CUDA_TRY(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
+    set_error("a kernel gave up a bounded wait (code %d)", v);
+    return LCQ_ERR_TIMEOUT;
+  }
+  return LCQ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,124 @@
+"""Host-side checks that need no GPU: the shared library loads and exports the whole C ABI,
+arguments are validated before the device is touched, and the GEMV work plan is sound."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+import locomp_b200 as L
+from locomp_b200 import _lib
+from locomp_b200.build import LIB_PATH, build, needs_build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _built():
+    if needs_build():
+        build()
+    assert os.path.exists(LIB_PATH)
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "locomp_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(lcq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    names = _declared_functions()
+    assert len(names) >= 12
+    handle = ctypes.CDLL(LIB_PATH)
+    for n in names:
+        assert hasattr(handle, n), f"{n} declared in the header but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert sorted(_lib.SIGNATURES) == names
+
+
+def test_version_and_status_strings():
+    lib = _lib.lib()
+    assert lib.lcq_version() >= 100
+    assert lib.lcq_status_string(0) == b"ok"
+    assert b"workspace" in lib.lcq_status_string(_lib.ERR_WORKSPACE)
+
+
+def test_c_abi_rejects_bad_problems_without_a_device():
+    lib = _lib.lib()
+    one = ctypes.c_void_p(256)
+    # K not a multiple of the group size
+    assert lib.lcq_matmul_int4(one, one, one, one, 1, 8, 40, 32, 0, 0, 0, 0, None, 0, None) == _lib.ERR_BAD_ARG
+    assert b"group_size" in lib.lcq_last_error()
+    # odd K for int4
+    assert lib.lcq_dequant_int4(one, one, one, 4, 7, 7, 0, 0, None) == _lib.ERR_BAD_ARG
+    # bad dtype code
+    assert lib.lcq_dequant_int8(one, one, one, 4, 8, 8, 9, 0, None) == _lib.ERR_BAD_ARG
+    # null pointers
+    assert lib.lcq_matmul_int8(None, one, one, one, 1, 8, 64, 32, 0, 0, 0, 0, None, 0, None) == _lib.ERR_BAD_ARG
+    # empty problems are fine and touch nothing
+    assert lib.lcq_matmul_int4(None, None, None, None, 0, 8, 64, 32, 0, 0, 0, 0, None, 0, None) == 0
+    assert lib.lcq_dequant_int4(None, None, None, 0, 64, 32, 0, 0, None) == 0
+    assert lib.lcq_matmul_workspace_bytes(4, 1, 8, 40, 32, 1, 1, 1, 0) == (1 << 64) - 1
+
+
+def test_algo_selection():
+    lib = _lib.lib()
+    sel = lib.lcq_matmul_select_algo
+    assert sel(4, 1, 2048, 2048, 32, _lib.F16, _lib.F16, _lib.F16) == _lib.ALGO_GEMV_TC
+    assert sel(4, 16, 2048, 8192, 32, _lib.F16, _lib.F16, _lib.F16) == _lib.ALGO_GEMV_TC
+    assert sel(4, 1, 1536, 576, 32, _lib.F16, _lib.F16, _lib.F16) == _lib.ALGO_SIMT      # K % 256 != 0
+    assert sel(4, 1, 4096, 4096, 32, _lib.F32, _lib.F32, _lib.F32) == _lib.ALGO_SIMT     # reference dtypes
+    assert sel(8, 1, 1536, 576, 576, _lib.F32, _lib.F32, _lib.F32) == _lib.ALGO_SIMT
+    assert lib.lcq_matmul_workspace_bytes(8, 1, 1536, 576, 576, 0, 0, 0, 0) == 0
+    assert lib.lcq_matmul_workspace_bytes(4, 1, 2048, 2048, 32, 1, 1, 1, 0) > 0
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+def test_gemv_plan_covers_every_tile_once(M):
+    lib = _lib.lib()
+    f = (ctypes.c_int * 8)()
+    for N in (1, 100, 128, 192, 1024, 2048, 8192, 16032, 49152, 128256):
+        for K in (256, 768, 2048, 8192, 28672):
+            for sms in (148, 132, 7, 1):
+                rc = lib.lcq_gemv_tc_plan_check(M, N, K, sms, f)
+                assert rc == 0, (M, N, K, sms, lib.lcq_last_error())
+                assert f[0] <= max(sms, f[2]) and f[6] <= 227 * 1024   # CTAs never wait on each other
+
+
+def test_python_validation_happens_before_the_gpu():
+    x = np.zeros(64, np.float32)
+    with pytest.raises(ValueError, match="K=64"):
+        L.gpu_matvec_int4(x, np.zeros((4, 31), np.uint8), np.zeros((4, 2), np.float32))
+    with pytest.raises(ValueError, match="scales"):
+        L.gpu_matvec_int4(x, np.zeros((4, 32), np.uint8), np.zeros((4, 3), np.float32))
+    with pytest.raises(TypeError, match="uint8"):
+        L.gpu_matvec_int4(x, np.zeros((4, 32), np.int8), np.zeros((4, 2), np.float32))
+    with pytest.raises(TypeError, match="int8"):
+        L.gpu_matvec_int8(x, np.zeros((4, 64), np.uint8), np.zeros((4, 2), np.float32))
+    with pytest.raises(ValueError, match="group_size"):
+        L.gpu_matvec_int8(x, np.zeros((4, 64), np.int8), np.zeros((4, 2), np.float32), group_size=48)
+    with pytest.raises(TypeError):
+        L.gpu_matvec_int4("nope", np.zeros((4, 32), np.uint8), np.zeros((4, 2), np.float32))
+    with pytest.raises(TypeError, match="float"):
+        L.gpu_matvec_int4(x.astype(np.int32), np.zeros((4, 32), np.uint8), np.zeros((4, 2), np.float32))
+    with pytest.raises(ValueError, match="bytes"):
+        L.gpu_dequant_int4(np.zeros(100, np.uint8), np.zeros(8, np.float32), 4, 64)
+    with pytest.raises(ValueError, match="grid"):
+        L.dequant_int4[(5,), (128,)](np.zeros(128, np.uint8), np.zeros(8, np.float32), np.zeros(256, np.float32),
+                                     64, 32, 2, 32)
+    with pytest.raises(ValueError, match="HALF_K"):
+        L.dequant_matvec_int4[(4,), (128,)](x, np.zeros(128, np.uint8), np.zeros(8, np.float32),
+                                            np.zeros(4, np.float32), 64, 31, 2, 32)
+    with pytest.raises(TypeError, match="missing"):
+        L.dequant_matvec_int8[(4,), (128,)](x, np.zeros(256, np.int8))
+    with pytest.raises(TypeError):
+        L.dequant_int8(np.zeros(4, np.int8))
+
+
+def test_no_cpu_fallback():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        L.gpu_matvec_int4(np.zeros(64, np.float32), np.zeros((4, 32), np.uint8), np.zeros((4, 2), np.float32))
