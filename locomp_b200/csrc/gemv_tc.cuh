@@ -43,6 +43,11 @@ constexpr int NCW = 8;                       // consumer warps, 16 rows each
 constexpr int NTHREADS = (NCW + 1) * 32;     // + 1 producer warp
 constexpr int X_SMEM_BYTES = 64 * 1024;      // budget for one k-range of activations
 constexpr int BAR_CONSUMERS = 1;             // named barrier id for the consumer warps
+// The workspace starts with a counter region of FIXED size so that it sits at the same place
+// for every problem: only the counters must be zero on entry (and are zero again on exit);
+// the partials behind them are scratch that successive calls may leave dirty.
+constexpr int MAX_ROW_BLOCKS = 16384;
+constexpr size_t COUNTER_BYTES = MAX_ROW_BLOCKS * sizeof(int);
 
 struct Params {
   const void* x;        // [M, K] fp16 or bf16
@@ -359,12 +364,12 @@ struct Plan {
   int grid;
   int MT;
   size_t smem_bytes;
-  size_t counters_bytes;   // rounded up to 256
+  size_t counters_bytes;   // COUNTER_BYTES, the same for every problem
   size_t workspace_bytes;  // counters + partials
 };
 
 inline bool supported(int M, int N, int K, int G, int x_dtype, int scale_dtype) {
-  return M >= 1 && M <= 16 && N >= 1 && K >= KT && (K % KT) == 0 && G == 32 &&
+  return M >= 1 && M <= 16 && N >= 1 && N <= MAX_ROW_BLOCKS * ROWS && K >= KT && (K % KT) == 0 && G == 32 &&
          (x_dtype == LCQ_F16 || x_dtype == LCQ_BF16) && scale_dtype == LCQ_F16;
 }
 
@@ -396,7 +401,7 @@ inline Plan make_plan(int M, int N, int K, int sm_count) {
   pl.grid = p.n_kr * p.ctas_per_kr;
   pl.MT = M <= 8 ? 1 : 2;
   pl.smem_bytes = smem_layout(M, 8 * pl.MT, p.S).total + 1024;
-  pl.counters_bytes = (static_cast<size_t>(p.n_rb) * sizeof(int) + 255) & ~static_cast<size_t>(255);
+  pl.counters_bytes = COUNTER_BYTES;
   pl.workspace_bytes = pl.counters_bytes +
                        static_cast<size_t>(p.n_rb) * p.n_kr * p.max_split * M * ROWS * sizeof(float);
   return pl;
