@@ -7,6 +7,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "../../include/locomp_b200.h"
@@ -106,6 +107,13 @@ __device__ __forceinline__ void mma_m16n8k16_f16(float (&d)[4], uint32_t a0, uin
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
       : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+
+// Four float zeros the optimiser cannot see through: kept live in one register quad, they can
+// be fed to an MMA as its C operand without being re-materialised before every use.
+__device__ __forceinline__ void opaque_zero4(float (&z)[4]) {
+  asm volatile("mov.f32 %0, 0f00000000;\n\tmov.f32 %1, 0f00000000;\n\tmov.f32 %2, 0f00000000;\n\tmov.f32 %3, 0f00000000;"
+               : "=f"(z[0]), "=f"(z[1]), "=f"(z[2]), "=f"(z[3]));
 }
 
 // ------------------------------------------------------------------ tensor-map encoding (host)

@@ -12,17 +12,24 @@
 // are four ready-made half2 A-operands holding elements (0,4) (1,5) (2,6) (3,7) of the 8
 // nibbles of a 32-bit word.  The activations are staged once per CTA into shared memory in
 // exactly that element order, with the (1,5) and (3,7) slots pre-divided by 16, so both
-// nibble positions come out scaled by 2^-24.  The zero point is folded in through the
-// accumulator input:  C = -8 * 2^-24 * sum_{k in g} x[m, k].  One 32-wide group is two
-// m16n8k16 MMAs, after which  acc += scale * D  (float32); the final result is acc * 2^24.
+// nibble positions come out scaled by 2^-24.  One 32-wide group is two m16n8k16 MMAs
+// giving D = 2^-24 * sum x*q, after which  acc += scale * D  in float32.
+//
+// The zero point (-8) is a separate, tiny contraction:  -8 * sum_g scale[n,g] * xsum[g,m]
+// with xsum[g,m] = sum_{k in g} x[m,k].  Per 256-wide tile that is ONE more MMA whose
+// A operand is the tile's 8 fp16 scales per row and whose B operand is -8*xsum split into
+// an fp16 high part (k slots 0-7) and an fp16 residual (k slots 8-15), accumulated in its
+// own float32 registers (B carries -8*xsum*2^-9 so it cannot overflow fp16).
+// Result: out = acc * 2^24 + corr * 2^9.
 //
 // Work decomposition.  A tile is 128 rows x 256 k (16 KB of packed weights + 2 KB of
 // scales, one TMA box each).  K is cut into n_kr ranges so that one range of x fits in
 // shared memory; the CTAs of a range split its tile sequence (row-block major) evenly,
 // stream-K style, so the last wave is never ragged.  A row block whose tiles were produced
 // by more than one CTA is combined through scratch: every contributor writes its float32
-// partial, bumps a per-row-block counter, and the last one sums all partials in a fixed
-// order, writes the output and resets the counter.  Nobody spins.
+// partial, bumps a counter (one per row block and 16-row warp slab, so warps never wait for
+// each other), and the last one sums all partials in a fixed order, writes the output and
+// resets the counter.  Nobody spins.
 //
 // HBM-bound: algorithmic bytes per call = N*K/2 + N*(K/32)*2 (+ 2*M*(K+N)).
 #pragma once
@@ -38,22 +45,29 @@ constexpr int GT = KT / 32;                  // groups per tile
 constexpr int W_BYTES = ROWS * (KT / 2);     // 16384, 128B-swizzled rows of 128 B
 constexpr int S_BYTES = ROWS * GT * 2;       // 2048, rows of 8 fp16 scales
 constexpr int STAGE_BYTES = W_BYTES + S_BYTES;
-constexpr int NSTAGES = 6;
 constexpr int NCW = 8;                       // consumer warps, 16 rows each
 constexpr int NTHREADS = (NCW + 1) * 32;     // + 1 producer warp
-constexpr int X_SMEM_BYTES = 64 * 1024;      // budget for one k-range of activations
 constexpr int BAR_CONSUMERS = 1;             // named barrier id for the consumer warps
 // The workspace starts with a counter region of FIXED size so that it sits at the same place
 // for every problem: only the counters must be zero on entry (and are zero again on exit);
 // the partials behind them are scratch that successive calls may leave dirty.
 constexpr int MAX_ROW_BLOCKS = 16384;
-constexpr size_t COUNTER_BYTES = MAX_ROW_BLOCKS * sizeof(int);
+constexpr size_t COUNTER_BYTES = static_cast<size_t>(MAX_ROW_BLOCKS) * NCW * sizeof(int);  // one per (row block, 16-row slab)
+
+// Per m-tile-count configuration: M <= 8 runs two CTAs per SM (16 consumer warps hide the
+// shared-memory and MMA latencies), M <= 16 one CTA with a deeper ring.
+template <int MT> struct Cfg;
+// XC_BYTES: shared memory left for the staged activations and zero-point operands.
+template <> struct Cfg<1> { static constexpr int NSTAGES = 4, CTAS_PER_SM = 2, XC_BYTES = 40000; };
+template <> struct Cfg<2> { static constexpr int NSTAGES = 6, CTAS_PER_SM = 1, XC_BYTES = 118000; };
+// bytes of x (M rows, exact) + zero-point operands (padded to 8*MT columns) per 256-wide tile
+__host__ __device__ inline int xc_bytes_per_tile(int M, int MT) { return GT * M * 64 + MT * 256; }
 
 struct Params {
   const void* x;        // [M, K] fp16 or bf16
   void* out;            // [M, N]
   float* partials;      // [n_rb][n_kr * max_split][M][ROWS]
-  int* counters;        // [n_rb], zero on entry, zero on exit
+  int* counters;        // [n_rb][NCW], zero on entry, zero on exit
   int M, N, K;
   int x_is_bf16;
   int n_rb;             // ceil(N / ROWS)
@@ -62,6 +76,7 @@ struct Params {
   int nst;              // K / 256
   int ctas_per_kr;      // CTAs working on one k-range
   int max_split;        // scratch slots per (row block, k-range)
+  int debug_mode;       // EXPERIMENT: 1 = consumers skip the math, 2 = no loads / no waits
 };
 
 struct Sched {          // the share of one k-range's tile sequence owned by one CTA
@@ -98,37 +113,40 @@ __host__ __device__ inline int contributors(const Params& p, int rb) {
   return total;
 }
 
-struct SmemLayout {
-  // offsets from the 1024-byte aligned base
-  int stages;   // NSTAGES * STAGE_BYTES
-  int xs;       // staged activations: [group][M][4] x 16 B
-  int cz;       // accumulator inputs: [group][MP] float
+struct SmemLayout {     // offsets from the 1024-byte aligned base
+  int xs;       // staged activations: [group][M][4] x 16 B, then one 64-byte block of zeros
+  int corr;     // zero-point operands: [tile][MT][8 m][4 t] x 8 B  (hi pair, lo pair)
   int bars;     // full[NSTAGES], empty[NSTAGES]
-  int flags;    // abort flag, last-arriver flag
+  int flags;    // abort flag
   int total;
 };
-__host__ __device__ inline SmemLayout smem_layout(int M, int MP, int S) {
+__host__ __device__ inline SmemLayout smem_layout(int nstages, int M, int MT, int S) {
   SmemLayout L;
-  L.stages = 0;
-  L.xs = NSTAGES * STAGE_BYTES;
-  const int groups = S * GT;
-  L.cz = L.xs + groups * M * 64;
-  L.bars = L.cz + groups * MP * 4;
-  L.bars = (L.bars + 15) & ~15;
-  L.flags = L.bars + 2 * NSTAGES * 8;
+  L.xs = nstages * STAGE_BYTES;
+  L.corr = L.xs + S * GT * M * 64 + 64;
+  L.bars = L.corr + S * MT * 8 * 4 * 8;
+  L.flags = L.bars + 2 * nstages * 8;
   L.total = L.flags + 16;
   return L;
 }
 
 template <typename T> __device__ __forceinline__ void store_out(T* out, long long idx, float v) { out[idx] = from_f32<T>(v); }
 
-template <int MT, typename OT>
-__global__ void __launch_bounds__(NTHREADS, 1)
+// MT: 8-wide m tiles (1 or 2).  NC: output columns each lane keeps per m tile (1 when M == 1,
+// where only column 0 exists, else 2).
+template <int MT, int NC, typename OT>
+__global__ void __launch_bounds__(NTHREADS, Cfg<MT>::CTAS_PER_SM)
 w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_s,
                   const Params p) {
   constexpr int MP = 8 * MT;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  constexpr int NSTAGES = Cfg<MT>::NSTAGES;
+  // Declared 1024-byte aligned (the 128-byte TMA swizzle needs it) and used directly, so the
+  // compiler keeps every access in the shared address space with 32-bit addressing.
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0u) {
+    if (threadIdx.x == 0) atomicExch(&g_device_status, 3);
+    return;
+  }
 
   const int kr = blockIdx.x % p.n_kr;
   const int j = blockIdx.x / p.n_kr;
@@ -136,18 +154,16 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
   if (j >= sch.G) return;  // whole CTA leaves together; nothing was started
   const long long t0 = tile_begin(sch, j), t1 = tile_begin(sch, j + 1);
 
-  const SmemLayout L = smem_layout(p.M, MP, p.S);
+  const SmemLayout L = smem_layout(NSTAGES, p.M, MT, p.S);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L.bars);
   uint64_t* empty_bar = full_bar + NSTAGES;
   volatile int* flag_abort = reinterpret_cast<volatile int*>(smem + L.flags);
-  volatile int* flag_last = flag_abort + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSTAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], NCW); }
     *flag_abort = 0;
-    *flag_last = 0;
     fence_barrier_init();
   }
   __syncthreads();
@@ -157,18 +173,18 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     if (lane == 0) {
       tma_prefetch_desc(&tmap_w);
       tma_prefetch_desc(&tmap_s);
-      bool dead = false;
       int it = 0;
       int rb = static_cast<int>(t0 / sch.S_kr);
       int ks = static_cast<int>(t0 - static_cast<long long>(rb) * sch.S_kr);
       for (long long t = t0; t < t1; ++t, ++it) {
         const int s = it % NSTAGES;
         const uint32_t ph = (it / NSTAGES) & 1;
-        if (!dead && *flag_abort) dead = true;
-        if (!dead && !mbar_wait_bounded(&empty_bar[s], ph ^ 1)) {
-          dead = true; *flag_abort = 1; atomicExch(&g_device_status, 1);
+        if (p.debug_mode == 2) break;
+        if (*flag_abort) break;
+        if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1)) {
+          *flag_abort = 1; atomicExch(&g_device_status, 1);
+          break;
         }
-        if (dead) break;
         const int kt = kr * p.S + ks;  // absolute k tile
         uint8_t* dst = smem + s * STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], STAGE_BYTES);
@@ -182,175 +198,254 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     const int ctid = threadIdx.x;            // 0..255
     const int g = lane >> 2, t4 = lane & 3;
     uint4* xs = reinterpret_cast<uint4*>(smem + L.xs);
-    float* cz = reinterpret_cast<float*>(smem + L.cz);
+    uint8_t* corr = smem + L.corr;
 
-    // ---- stage this k-range of x: permuted element order, fp16, high-nibble slots / 16
+    // ---- stage this k-range of x: permuted element order, fp16, high-nibble slots / 16;
+    //      and the zero-point operands -8 * xsum * 2^-9 as fp16 (high part, residual)
     {
       const int oct_per_row = sch.S_kr * (KT / 8);
       const int total = p.M * oct_per_row;
       const long long kbase = static_cast<long long>(kr) * p.S * KT;
-      for (int i = ctid; i < sch.S_kr * GT * MP; i += NCW * 32) cz[i] = 0.0f;
+      const int zero16 = (L.bars - L.xs) / 16;
+      for (int i = ctid; i < zero16; i += NCW * 32) xs[i] = make_uint4(0u, 0u, 0u, 0u);
       named_bar_sync(BAR_CONSUMERS, NCW * 32);
-      for (int base = 0; base < total; base += NCW * 32) {
-        const int idx = base + ctid;
-        const bool valid = idx < total;
-        const int m = valid ? idx / oct_per_row : 0;
-        const int o = valid ? idx - m * oct_per_row : 0;
-        float v[8];
-        if (valid) {
-          const long long off = static_cast<long long>(m) * p.K + kbase + 8 * o;
-          if (p.x_is_bf16) load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.x) + off, v);
-          else load8<__half>(static_cast<const __half*>(p.x) + off, v);
-        } else {
+      constexpr int U = 4;   // independent 16-byte loads in flight per thread
+      for (int base = 0; base < total; base += U * NCW * 32) {
+        uint4 raw[U];
+        int mm[U], oo[U];
+        bool ok[U];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+        for (int u = 0; u < U; ++u) {
+          const int idx = base + u * NCW * 32 + ctid;
+          ok[u] = idx < total;
+          mm[u] = ok[u] ? idx / oct_per_row : 0;
+          oo[u] = ok[u] ? idx - mm[u] * oct_per_row : 0;
+          raw[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (ok[u]) {
+            const long long off = static_cast<long long>(mm[u]) * p.K + kbase + 8 * oo[u];
+            raw[u] = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.x) + off));
+          }
         }
-        float sum = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        if (valid) {
-          const __half2 h0 = __floats2half2_rn(v[0], v[4]);
-          const __half2 h1 = __floats2half2_rn(v[1] * 0.0625f, v[5] * 0.0625f);
-          const __half2 h2 = __floats2half2_rn(v[2], v[6]);
-          const __half2 h3 = __floats2half2_rn(v[3] * 0.0625f, v[7] * 0.0625f);
-          uint4 q;
-          q.x = *reinterpret_cast<const uint32_t*>(&h0); q.y = *reinterpret_cast<const uint32_t*>(&h1);
-          q.z = *reinterpret_cast<const uint32_t*>(&h2); q.w = *reinterpret_cast<const uint32_t*>(&h3);
-          const int grp = o >> 2;
-          xs[(grp * p.M + m) * 4 + (o & 3)] = q;
-          if ((o & 3) == 0) cz[grp * MP + m] = -sum * 4.76837158203125e-07f;  // -8 * 2^-24
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          float v[8];
+          const uint32_t* rw = reinterpret_cast<const uint32_t*>(&raw[u]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            if (p.x_is_bf16) {
+              v[2 * e] = __uint_as_float(rw[e] << 16);
+              v[2 * e + 1] = __uint_as_float(rw[e] & 0xFFFF0000u);
+            } else {
+              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&rw[e]));
+              v[2 * e] = f.x; v[2 * e + 1] = f.y;
+            }
+          }
+          float sum = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+          sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+          if (ok[u]) {
+            const int m = mm[u], o = oo[u];
+            const __half2 h0 = __floats2half2_rn(v[0], v[4]);
+            const __half2 h1 = __floats2half2_rn(v[1] * 0.0625f, v[5] * 0.0625f);
+            const __half2 h2 = __floats2half2_rn(v[2], v[6]);
+            const __half2 h3 = __floats2half2_rn(v[3] * 0.0625f, v[7] * 0.0625f);
+            uint4 q;
+            q.x = *reinterpret_cast<const uint32_t*>(&h0); q.y = *reinterpret_cast<const uint32_t*>(&h1);
+            q.z = *reinterpret_cast<const uint32_t*>(&h2); q.w = *reinterpret_cast<const uint32_t*>(&h3);
+            const int grp = o >> 2;
+            xs[(grp * p.M + m) * 4 + (o & 3)] = q;
+            if ((o & 3) == 0) {
+              const float zp = -0.015625f * sum;   // -8 * xsum * 2^-9: stays inside fp16 range for any fp16 x
+              const __half hi = __float2half_rn(zp);
+              const __half lo = __float2half_rn(zp - __half2float(hi));
+              const int tile = grp >> 3, gi = grp & 7;
+              uint8_t* cp = corr + ((((tile * MT + (m >> 3)) * 8 + (m & 7)) * 4 + (gi >> 1)) * 8) + (gi & 1) * 2;
+              *reinterpret_cast<__half*>(cp) = hi;
+              *reinterpret_cast<__half*>(cp + 4) = lo;
+            }
+          }
         }
       }
       named_bar_sync(BAR_CONSUMERS, NCW * 32);
     }
 
-    float acc[MT][4];
-#pragma unroll
-    for (int jm = 0; jm < MT; ++jm) { acc[jm][0] = acc[jm][1] = acc[jm][2] = acc[jm][3] = 0.0f; }
-
-    const int r0 = warp * 16 + g;
-    const int swz = g & 7;
-    bool has_m[MT];
-    const uint4* xs_lane[MT];
-    const float2* cz_lane[MT];
+    float acc[MT][4], cor[MT][4];
 #pragma unroll
     for (int jm = 0; jm < MT; ++jm) {
-      has_m[jm] = (8 * jm + g) < p.M;
-      xs_lane[jm] = xs + (has_m[jm] ? (8 * jm + g) * 4 + t4 : 0);
-      cz_lane[jm] = reinterpret_cast<const float2*>(cz + 8 * jm + 2 * t4);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { acc[jm][e] = 0.0f; cor[jm][e] = 0.0f; }
     }
 
+    float zero4[4];
+    opaque_zero4(zero4);
+
+    const int r0 = warp * 16 + g;
+    // byte offset of (row r0, word t4) inside a stage with the row's swizzle folded in:
+    // chunk c of that row sits at  lane_off ^ (c << 4)   (rows r0 and r0+8 share r & 7)
+    const uint32_t lane_off = static_cast<uint32_t>(r0 * 128 + 4 * t4) ^ (static_cast<uint32_t>(g & 7) << 4);
+    // x fragment of lane (g, t4) for m tile jm: row m = 8*jm + g of group grp sits at
+    // xs[(grp*M + m)*4 + t4]; lanes whose m does not exist read the block of zeros (stride 0)
+    const uint4* xs_lane[MT];
+    int xs_stride[MT];
+#pragma unroll
+    for (int jm = 0; jm < MT; ++jm) {
+      const bool has = (8 * jm + g) < p.M;
+      xs_lane[jm] = has ? xs + (8 * jm + g) * 4 + t4 : xs + p.S * GT * p.M * 4;
+      xs_stride[jm] = has ? p.M * 4 : 0;
+    }
+    const uint2* corr_lane = reinterpret_cast<const uint2*>(corr) + g * 4 + t4;  // + (tile*MT + jm)*32
+
     bool dead = false;
-    int it = 0;
     int rb = static_cast<int>(t0 / sch.S_kr);
     int ks = static_cast<int>(t0 - static_cast<long long>(rb) * sch.S_kr);
-    for (long long t = t0; t < t1; ++t, ++it) {
-      const int s = it % NSTAGES;
-      const uint32_t ph = (it / NSTAGES) & 1;
-
-      if (!dead && *flag_abort) dead = true;
-      if (!dead && !mbar_wait_bounded(&full_bar[s], ph)) {
-        dead = true; *flag_abort = 1; atomicExch(&g_device_status, 2);
+    const int n_tiles = static_cast<int>(t1 - t0);
+    int s = 0;
+    uint32_t ph = 0;
+    for (int ti = 0; ti < n_tiles; ++ti) {
+      const long long t = t0 + ti;
+      if (!dead && p.debug_mode != 2) {
+        if (*flag_abort || !mbar_wait_bounded(&full_bar[s], ph)) {
+          dead = true; *flag_abort = 1; atomicExch(&g_device_status, 2);
+        }
       }
-      if (!dead) {
+      if (!dead && p.debug_mode != 1) {
         const uint8_t* ws = smem + s * STAGE_BYTES;
-        const uint32_t* rowA = reinterpret_cast<const uint32_t*>(ws + r0 * 128) + t4;
-        const uint32_t* rowB = reinterpret_cast<const uint32_t*>(ws + (r0 + 8) * 128) + t4;
-        const uint4 sA = *reinterpret_cast<const uint4*>(ws + W_BYTES + r0 * 16);
-        const uint4 sB = *reinterpret_cast<const uint4*>(ws + W_BYTES + (r0 + 8) * 16);
-        const __half* hA = reinterpret_cast<const __half*>(&sA);
-        const __half* hB = reinterpret_cast<const __half*>(&sB);
-        const int gbase = ks * GT;
+        const uint32_t* srA = reinterpret_cast<const uint32_t*>(ws + W_BYTES + r0 * 16);
+        const uint32_t* srB = reinterpret_cast<const uint32_t*>(ws + W_BYTES + (r0 + 8) * 16);
+        const uint4 sA = *reinterpret_cast<const uint4*>(srA);
+        const uint4 sB = *reinterpret_cast<const uint4*>(srB);
+        float scA[GT], scB[GT];   // the tile's 8 scales of rows r0 and r0+8
+        {
+          const uint32_t wA[4] = {sA.x, sA.y, sA.z, sA.w}, wB[4] = {sB.x, sB.y, sB.z, sB.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&wA[i]));
+            const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&wB[i]));
+            scA[2 * i] = fa.x; scA[2 * i + 1] = fa.y; scB[2 * i] = fb.x; scB[2 * i + 1] = fb.y;
+          }
+        }
+        const uint4* xp[MT];
+#pragma unroll
+        for (int jm = 0; jm < MT; ++jm) xp[jm] = xs_lane[jm] + ks * GT * xs_stride[jm];
 #pragma unroll
         for (int c = 0; c < GT; ++c) {
-          const int cs = (c ^ swz) * 4;
-          const uint32_t wa = rowA[cs], wb = rowB[cs];
+          const uint32_t off = lane_off ^ (static_cast<uint32_t>(c) << 4);
+          const uint32_t wa = *reinterpret_cast<const uint32_t*>(ws + off);
+          const uint32_t wb = *reinterpret_cast<const uint32_t*>(ws + off + 1024);
           const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
-          const float s_a = __half2float(hA[c]), s_b = __half2float(hB[c]);
 #pragma unroll
           for (int jm = 0; jm < MT; ++jm) {
-            uint4 bx = make_uint4(0u, 0u, 0u, 0u);
-            if (has_m[jm]) bx = xs_lane[jm][(gbase + c) * p.M * 4];
-            const float2 ci = cz_lane[jm][(gbase + c) * (MP / 2)];
-            const float cin[4] = {ci.x, ci.y, ci.x, ci.y};
+            const uint4 bx = *xp[jm];
+            xp[jm] += xs_stride[jm];
             float d[4];
             mma_m16n8k16_f16(d, wa & 0x000F000Fu, wb & 0x000F000Fu, wa & 0x00F000F0u, wb & 0x00F000F0u,
-                             bx.x, bx.y, cin);
+                             bx.x, bx.y, zero4);
             mma_m16n8k16_f16(d, wa8 & 0x000F000Fu, wb8 & 0x000F000Fu, wa8 & 0x00F000F0u, wb8 & 0x00F000F0u,
                              bx.z, bx.w, d);
-            acc[jm][0] = fmaf(s_a, d[0], acc[jm][0]);
-            acc[jm][1] = fmaf(s_a, d[1], acc[jm][1]);
-            acc[jm][2] = fmaf(s_b, d[2], acc[jm][2]);
-            acc[jm][3] = fmaf(s_b, d[3], acc[jm][3]);
+            acc[jm][0] = fmaf(scA[c], d[0], acc[jm][0]);
+            acc[jm][2] = fmaf(scB[c], d[2], acc[jm][2]);
+            if (NC == 2) {
+              acc[jm][1] = fmaf(scA[c], d[1], acc[jm][1]);
+              acc[jm][3] = fmaf(scB[c], d[3], acc[jm][3]);
+            }
           }
+        }
+        // zero point of the whole tile: A = the rows' 8 scales (k slots 0-7 and again 8-15),
+        // B = (-8*xsum*2^-9) high parts | residuals
+        const uint32_t sa_w = srA[t4], sb_w = srB[t4];
+#pragma unroll
+        for (int jm = 0; jm < MT; ++jm) {
+          const uint2 cb = corr_lane[(ks * MT + jm) * 32];
+          mma_m16n8k16_f16(cor[jm], sa_w, sb_w, sa_w, sb_w, cb.x, cb.y, cor[jm]);
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[s]);  // also in the dead state, so the producer never stalls on us
+      const int s_used = s;
+      (void)s_used;
+      if (++s == NSTAGES) { s = 0; ph ^= 1; }
 
-      // ---- end of this CTA's share of row block rb: flush
+      // ---- end of this CTA's share of row block rb: flush.  Each warp settles its own
+      //      16-row slab, so no CTA-wide barrier is needed and the other warps keep streaming.
       if (ks == sch.S_kr - 1 || t == t1 - 1) {
-        const int n_contrib = contributors(p, rb);
         const int nA = rb * ROWS + r0, nB = nA + 8;
-        if (n_contrib == 1) {
+        float y[MT][4];
+#pragma unroll
+        for (int jm = 0; jm < MT; ++jm) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) y[jm][e] = fmaf(acc[jm][e], 16777216.0f, cor[jm][e] * 512.0f);
+        }
+        const long long rb_t0 = static_cast<long long>(rb) * sch.S_kr;
+        const bool whole = p.n_kr == 1 && rb_t0 >= t0 && rb_t0 + sch.S_kr <= t1;
+        if (whole) {
           OT* out = static_cast<OT*>(p.out);
 #pragma unroll
           for (int jm = 0; jm < MT; ++jm) {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
+            for (int e = 0; e < NC; ++e) {
               const int m = 8 * jm + 2 * t4 + e;
               if (m < p.M) {
-                if (nA < p.N) store_out(out, static_cast<long long>(m) * p.N + nA, acc[jm][e] * 16777216.0f);
-                if (nB < p.N) store_out(out, static_cast<long long>(m) * p.N + nB, acc[jm][2 + e] * 16777216.0f);
+                if (nA < p.N) store_out(out, static_cast<long long>(m) * p.N + nA, y[jm][e]);
+                if (nB < p.N) store_out(out, static_cast<long long>(m) * p.N + nB, y[jm][2 + e]);
               }
             }
           }
         } else {
-          int j0, j1;
+          // contributors: identical for every full-length k-range, the last range may differ
+          int j0, j1, c_full, c_last;
           cover(sch, rb, j0, j1);
+          {
+            int a0, a1;
+            const Sched sf = make_sched(p, 0);
+            cover(sf, rb, a0, a1);
+            c_full = a1 - a0 + 1;
+            const Sched sl = make_sched(p, p.n_kr - 1);
+            cover(sl, rb, a0, a1);
+            c_last = a1 - a0 + 1;
+          }
+          const int n_contrib = (p.n_kr - 1) * c_full + c_last;
           const int slot = kr * p.max_split + (j - j0);
-          float* part = p.partials + (static_cast<long long>(rb) * p.n_kr * p.max_split + slot) * p.M * ROWS;
+          const long long slot_elems = static_cast<long long>(p.M) * ROWS;
+          float* rb_part = p.partials + static_cast<long long>(rb) * p.n_kr * p.max_split * slot_elems;
+          float* part = rb_part + slot * slot_elems;
 #pragma unroll
           for (int jm = 0; jm < MT; ++jm) {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
+            for (int e = 0; e < NC; ++e) {
               const int m = 8 * jm + 2 * t4 + e;
               if (m < p.M) {
-                __stcg(part + m * ROWS + r0, acc[jm][e] * 16777216.0f);
-                __stcg(part + m * ROWS + r0 + 8, acc[jm][2 + e] * 16777216.0f);
+                __stcg(part + m * ROWS + r0, y[jm][e]);
+                __stcg(part + m * ROWS + r0 + 8, y[jm][2 + e]);
               }
             }
           }
           __threadfence();
-          named_bar_sync(BAR_CONSUMERS, NCW * 32);
-          if (ctid == 0) {
-            const int old = atomicAdd(p.counters + rb, 1);
-            *flag_last = (old == n_contrib - 1) ? 1 : 0;
-          }
-          named_bar_sync(BAR_CONSUMERS, NCW * 32);
-          if (*flag_last) {
+          __syncwarp();
+          int last = 0;
+          if (lane == 0) last = (atomicAdd(p.counters + rb * NCW + warp, 1) == n_contrib - 1) ? 1 : 0;
+          last = __shfl_sync(0xffffffffu, last, 0);
+          if (last) {
             __threadfence();
             OT* out = static_cast<OT*>(p.out);
-            const float* rb_part = p.partials + static_cast<long long>(rb) * p.n_kr * p.max_split * p.M * ROWS;
-            for (int idx = ctid; idx < p.M * ROWS; idx += NCW * 32) {
-              const int m = idx / ROWS, r = idx - m * ROWS;
+            for (int idx = lane; idx < p.M * 16; idx += 32) {
+              const int m = idx >> 4, r = warp * 16 + (idx & 15);
+              const float* src = rb_part + m * ROWS + r;
               float sum = 0.0f;
               for (int kk = 0; kk < p.n_kr; ++kk) {
-                const Sched s2 = make_sched(p, kk);
-                int a0, a1;
-                cover(s2, rb, a0, a1);
-                for (int c = 0; c <= a1 - a0; ++c)
-                  sum += __ldcg(rb_part + (static_cast<long long>(kk) * p.max_split + c) * p.M * ROWS + idx);
+                const int cnt = (kk == p.n_kr - 1) ? c_last : c_full;
+                for (int c = 0; c < cnt; ++c) sum += __ldcg(src + (kk * p.max_split + c) * slot_elems);
               }
               const int n = rb * ROWS + r;
               if (n < p.N) store_out(out, static_cast<long long>(m) * p.N + n, sum);
             }
-            if (ctid == 0) p.counters[rb] = 0;
+            if (lane == 0) p.counters[rb * NCW + warp] = 0;
           }
-          named_bar_sync(BAR_CONSUMERS, NCW * 32);  // flag_last is reused by the next flush
         }
 #pragma unroll
-        for (int jm = 0; jm < MT; ++jm) { acc[jm][0] = acc[jm][1] = acc[jm][2] = acc[jm][3] = 0.0f; }
+        for (int jm = 0; jm < MT; ++jm) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { acc[jm][e] = 0.0f; cor[jm][e] = 0.0f; }
+        }
       }
       if (++ks == sch.S_kr) { ks = 0; ++rb; }
     }
@@ -378,13 +473,17 @@ inline Plan make_plan(int M, int N, int K, int sm_count) {
   memset(&pl, 0, sizeof(pl));
   Params& p = pl.p;
   p.M = M; p.N = N; p.K = K;
+  pl.MT = M <= 8 ? 1 : 2;
+  const int nstages = pl.MT == 1 ? Cfg<1>::NSTAGES : Cfg<2>::NSTAGES;
+  const int ctas_per_sm = pl.MT == 1 ? Cfg<1>::CTAS_PER_SM : Cfg<2>::CTAS_PER_SM;
+  const int xc_bytes = pl.MT == 1 ? Cfg<1>::XC_BYTES : Cfg<2>::XC_BYTES;
   p.n_rb = (N + ROWS - 1) / ROWS;
   p.nst = K / KT;
-  const int s_max = X_SMEM_BYTES / (M * KT * 2);
+  const int s_max = xc_bytes / xc_bytes_per_tile(M, pl.MT);
   p.n_kr = (p.nst + s_max - 1) / s_max;
   p.S = (p.nst + p.n_kr - 1) / p.n_kr;
   p.n_kr = (p.nst + p.S - 1) / p.S;           // drop empty trailing ranges
-  p.ctas_per_kr = sm_count / p.n_kr;
+  p.ctas_per_kr = (sm_count * ctas_per_sm) / p.n_kr;
   if (p.ctas_per_kr < 1) p.ctas_per_kr = 1;
   const long long T = static_cast<long long>(p.n_rb) * p.S;
   if (p.ctas_per_kr > T) p.ctas_per_kr = static_cast<int>(T);
@@ -399,27 +498,36 @@ inline Plan make_plan(int M, int N, int K, int sm_count) {
   }
   p.max_split = max_split;
   pl.grid = p.n_kr * p.ctas_per_kr;
-  pl.MT = M <= 8 ? 1 : 2;
-  pl.smem_bytes = smem_layout(M, 8 * pl.MT, p.S).total + 1024;
+  pl.smem_bytes = smem_layout(nstages, M, pl.MT, p.S).total;
   pl.counters_bytes = COUNTER_BYTES;
   pl.workspace_bytes = pl.counters_bytes +
                        static_cast<size_t>(p.n_rb) * p.n_kr * p.max_split * M * ROWS * sizeof(float);
   return pl;
 }
 
-template <int MT, typename OT>
+template <int MT, int NC, typename OT>
 int launch_t(const Plan& pl, const CUtensorMap& tw, const CUtensorMap& ts, cudaStream_t stream) {
-  auto kern = w4a16_gemv_kernel<MT, OT>;
+  auto kern = w4a16_gemv_kernel<MT, NC, OT>;
   static thread_local int configured_device = -1;  // per (thread, template instance)
   int dev = 0;
   LCQ_CUDA_TRY(cudaGetDevice(&dev));
   if (configured_device != dev) {
-    LCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    LCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (227 * 1024) / Cfg<MT>::CTAS_PER_SM - 1024));
+    LCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                      cudaSharedmemCarveoutMaxShared));
     configured_device = dev;
   }
   kern<<<pl.grid, NTHREADS, pl.smem_bytes, stream>>>(tw, ts, pl.p);
   LCQ_CUDA_TRY(cudaGetLastError());
   return LCQ_OK;
+}
+
+template <typename OT>
+int launch_o(const Plan& pl, const CUtensorMap& tw, const CUtensorMap& ts, cudaStream_t stream) {
+  if (pl.MT == 2) return launch_t<2, 2, OT>(pl, tw, ts, stream);
+  if (pl.p.M == 1) return launch_t<1, 1, OT>(pl, tw, ts, stream);
+  return launch_t<1, 2, OT>(pl, tw, ts, stream);
 }
 
 inline int launch(const void* x, const void* w, const void* s, void* out, int M, int N, int K, int x_dtype,
@@ -437,6 +545,7 @@ inline int launch(const void* x, const void* w, const void* s, void* out, int M,
   pl.p.x = x;
   pl.p.out = out;
   pl.p.x_is_bf16 = (x_dtype == LCQ_BF16);
+  { const char* e = getenv("LCQ_GEMV_DEBUG_MODE"); pl.p.debug_mode = e ? atoi(e) : 0; }
   pl.p.counters = static_cast<int*>(workspace);
   pl.p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + pl.counters_bytes);
   CUtensorMap tw, ts;
@@ -446,15 +555,12 @@ inline int launch(const void* x, const void* w, const void* s, void* out, int M,
   rc = encode_tmap_2d(&ts, 1, s, static_cast<uint64_t>(K) / 32, static_cast<uint64_t>(N),
                       static_cast<uint64_t>(K) / 16, GT, ROWS, 0);
   if (rc != LCQ_OK) return rc;
-#define LCQ_GEMV_TC_CASE(MT_)                                                                 \
-  switch (out_dtype) {                                                                        \
-    case LCQ_F32: return launch_t<MT_, float>(pl, tw, ts, stream);                            \
-    case LCQ_F16: return launch_t<MT_, __half>(pl, tw, ts, stream);                           \
-    case LCQ_BF16: return launch_t<MT_, __nv_bfloat16>(pl, tw, ts, stream);                   \
-    default: break;                                                                           \
+  switch (out_dtype) {
+    case LCQ_F32: return launch_o<float>(pl, tw, ts, stream);
+    case LCQ_F16: return launch_o<__half>(pl, tw, ts, stream);
+    case LCQ_BF16: return launch_o<__nv_bfloat16>(pl, tw, ts, stream);
+    default: break;
   }
-  if (pl.MT == 1) { LCQ_GEMV_TC_CASE(1) } else { LCQ_GEMV_TC_CASE(2) }
-#undef LCQ_GEMV_TC_CASE
   set_error("w4a16 gemv: bad out_dtype %d", out_dtype);
   return LCQ_ERR_BAD_ARG;
 }

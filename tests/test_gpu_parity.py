@@ -219,9 +219,10 @@ def test_w4a16_bf16_activations_and_linearity():
     yb = L.quantized_matmul(xb.cuda(), wd, sd, 32)
     assert yb.dtype == torch.bfloat16
     _check16(yb.float().cpu().numpy(), ref)
-    # exact linearity in x for power-of-two factors (float32 output)
+    # linearity in x for power-of-two factors (float32 output): exact up to the fp16 residual of
+    # the zero-point term, which may fall into the subnormal range
     y2 = L.quantized_matmul((xb * 2).cuda(), wd, sd, 32, out_dtype="f32")
-    assert torch.equal(y2, y * 2)
+    torch.testing.assert_close(y2, y * 2, rtol=1e-5, atol=1e-5)
 
 
 def test_w4a16_zero_point_and_extremes():
