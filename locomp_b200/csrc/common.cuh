@@ -24,6 +24,10 @@ int cuda_fail(cudaError_t e, const char* what); // stores the message, returns L
     if (_e != cudaSuccess) return ::lcq::cuda_fail(_e, #expr);        \
   } while (0)
 
+// Every workspace starts with this many bytes of counters that must be zero between calls;
+// whatever follows is scratch that calls may leave dirty.
+constexpr size_t kWorkspaceCounterBytes = 512 * 1024;
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 // Device status word: set to a non-zero code by a kernel whose bounded wait expired.
@@ -69,14 +73,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait: returns false (and the caller must bail out) if the phase never completes.
-// Each try_wait already blocks for a hardware-defined interval, so the limit is generous.
-constexpr uint32_t kWaitLimit = 1u << 22;
+// Bounded wait: returns false (and the caller must unwind) if the phase does not complete
+// within about two seconds of wall-clock time.  try_wait itself suspends the thread for a
+// hardware-defined interval, so the loop is not a hot spin.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
   }
-  return false;
 }
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

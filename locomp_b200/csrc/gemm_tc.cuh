@@ -1,14 +1,428 @@
-// W4A16 prefill GEMM on tcgen05 tensor cores (placeholder until the kernel lands).
+// W4A16 prefill GEMM (M > 16) on 5th-generation tensor cores: tcgen05.mma with the
+// accumulator AND the dequantised weight operand in tensor memory.
+//
+//   out[m, n] = sum_k x[m, k] * (nib(n, k) - 8) * scales[n, k / 32]      (float32 accumulate)
+//
+// Orientation ("swap A/B"): the MMA's M dimension is the weight row n, its N dimension the
+// activation row m:   D[128 n x BM m] += Wdq[128 n x 64 k] * X^T[64 k x BM m].
+//   * X tiles [BM x 64] fp16 arrive by TMA (128-byte swizzle) and are the shared-memory B operand.
+//   * Packed int4 tiles [128 n x 256 k] (+ their fp16 scales) arrive by TMA; eight dequant
+//     warps turn them into fp16 (exactly RN((q - 8) * s)) in registers and write them with
+//     tcgen05.st into a ring of TMEM slots that the MMA reads as its A operand.  The packed
+//     weights therefore cross shared memory once (0.5 B/weight) and never as 2-byte values.
+//   * One thread issues the MMAs; tcgen05.commit releases X stages and TMEM slots and, after
+//     the last k tile, hands the accumulator to four epilogue warps (tcgen05.ld -> global).
+// TMEM map (512 columns): [0, 256) accumulator, [256, 384) four A slots of 32 columns
+// (64 k as packed fp16 pairs).  Weight tiles are fp16 because bf16's 8-bit significand
+// cannot hold (q-8)*s within the 1e-2 output tolerance; bf16 activations are converted to
+// fp16 by a small pre-pass into the caller's workspace.
+//
+// Tensor-bound: 2*M*N*K flops per call against the dense 16-bit tensor peak.
+// Every mbarrier wait is bounded; on expiry the kernel records a status code and unwinds.
 #pragma once
 #include "common.cuh"
+
 namespace lcq {
 namespace gemm_tc {
-inline bool supported(int, int, int, int, int, int) { return false; }
-inline size_t workspace_bytes(int, int, int) { return 0; }
-inline int launch(const void*, const void*, const void*, void*, int, int, int, int, int, void*, size_t, int,
-                  cudaStream_t) {
-  set_error("GEMM_TC is not built");
-  return LCQ_ERR_UNSUPPORTED;
+
+constexpr int BN = 128;                 // weight rows per tile (MMA M)
+constexpr int BK = 64;                  // k per MMA stage (one 128-byte swizzle row of fp16)
+constexpr int WK = 256;                 // k per packed-weight stage
+constexpr int W_STAGE = BN * (WK / 2);  // 16384
+constexpr int S_STAGE = BN * (WK / 32) * 2;   // 2048
+constexpr int WS_STAGE = W_STAGE + S_STAGE;
+constexpr int NXS = 4;                  // X stages
+constexpr int NWS = 2;                  // packed-weight stages
+constexpr int NAS = 4;                  // TMEM A slots
+constexpr int A_COL0 = 256;             // first TMEM column of the A ring
+constexpr int A_SLOT_COLS = 32;
+constexpr int TMEM_COLS = 512;
+constexpr int NTHREADS = 512;
+constexpr int WARP_TMA = 4, WARP_MMA = 5, WARP_DQ0 = 8, N_DQ_WARPS = 8;
+
+// ---------------------------------------------------------------- tcgen05 wrappers
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem descriptor]
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile of 128-byte rows, 128-byte swizzle,
+// 1024 bytes between 8-row groups.
+__device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);   // start address
+  d |= static_cast<uint64_t>(1) << 16;                        // leading byte offset (unused for swizzled K-major)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                        // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2) << 61;                        // 128-byte swizzle
+  return d;
+}
+// kind::f16 instruction descriptor: D=f32, A=B=f16, both K-major, M=128, N=bm.
+__host__ __device__ inline uint32_t make_idesc(int bm) {
+  return (1u << 4) | (static_cast<uint32_t>(bm >> 3) << 17) | (static_cast<uint32_t>(BN >> 4) << 24);
+}
+
+struct Params {
+  void* out;            // [M, N]
+  int M, N, K;
+  int bm;               // activation rows per tile (MMA N): multiple of 32, <= 256
+  int n_tiles_n, n_tiles_m;
+  int out_dtype;
+};
+
+struct Smem {           // offsets from the 1024-byte aligned dynamic shared memory base
+  int x;                // NXS stages of bm x 128 B
+  int w;                // NWS stages of WS_STAGE
+  int bars;
+  int tmem_slot;
+  int flags;
+  int total;
+};
+__host__ __device__ inline Smem smem_map(int bm) {
+  Smem s;
+  s.x = 0;
+  s.w = NXS * bm * 128;
+  s.bars = s.w + NWS * WS_STAGE;
+  // full_x, empty_x [NXS]; full_w, empty_w [NWS]; full_a, empty_a [NAS]; full_d, empty_d
+  s.tmem_slot = s.bars + (2 * NXS + 2 * NWS + 2 * NAS + 2) * 8;
+  s.flags = s.tmem_slot + 8;
+  s.total = s.flags + 8;
+  return s;
+}
+
+// RN((q - 8) * s) for the 8 nibbles of a word, as 4 half2 in natural k order.
+__device__ __forceinline__ void dequant_word(uint32_t w, __half2 s2, uint32_t (&o)[4]) {
+  const __half2 k1032 = __half2half2(__ushort_as_half(0x6408));   // 1032.0
+  const __half2 k16th = __half2half2(__ushort_as_half(0x2C00));   // 1/16
+  const __half2 km72 = __half2half2(__ushort_as_half(0xD480));    // -72.0
+  const uint32_t w8 = w >> 8;
+  uint32_t l0 = (w & 0x000F000Fu) | 0x64006400u;     // 1024 + (e0, e4)
+  uint32_t h0 = (w & 0x00F000F0u) | 0x64006400u;     // 1024 + 16*(e1, e5)
+  uint32_t l1 = (w8 & 0x000F000Fu) | 0x64006400u;    // 1024 + (e2, e6)
+  uint32_t h1 = (w8 & 0x00F000F0u) | 0x64006400u;    // 1024 + 16*(e3, e7)
+  __half2 p0 = __hsub2(*reinterpret_cast<__half2*>(&l0), k1032);
+  __half2 p1 = __hfma2(*reinterpret_cast<__half2*>(&h0), k16th, km72);
+  __half2 p2 = __hsub2(*reinterpret_cast<__half2*>(&l1), k1032);
+  __half2 p3 = __hfma2(*reinterpret_cast<__half2*>(&h1), k16th, km72);
+  p0 = __hmul2(p0, s2); p1 = __hmul2(p1, s2); p2 = __hmul2(p2, s2); p3 = __hmul2(p3, s2);
+  const uint32_t u0 = *reinterpret_cast<uint32_t*>(&p0), u1 = *reinterpret_cast<uint32_t*>(&p1);
+  const uint32_t u2 = *reinterpret_cast<uint32_t*>(&p2), u3 = *reinterpret_cast<uint32_t*>(&p3);
+  o[0] = __byte_perm(u0, u1, 0x5410);   // (e0, e1)
+  o[1] = __byte_perm(u2, u3, 0x5410);   // (e2, e3)
+  o[2] = __byte_perm(u0, u1, 0x7632);   // (e4, e5)
+  o[3] = __byte_perm(u2, u3, 0x7632);   // (e6, e7)
+}
+
+// Bounded wait whose verdict is the same in every lane, so warp-aligned instructions that
+// follow it never run with a partial warp.
+__device__ __forceinline__ bool warp_wait(volatile int* flag_abort, uint64_t* bar, uint32_t parity) {
+  const bool ok = (*flag_abort == 0) && mbar_wait_bounded(bar, parity);
+  return __all_sync(0xffffffffu, ok);
+}
+
+template <typename OT>
+__global__ void __launch_bounds__(NTHREADS, 1)
+w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                  const __grid_constant__ CUtensorMap tmap_s, const Params p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0u) {
+    if (threadIdx.x == 0) atomicExch(&g_device_status, 13);
+    return;
+  }
+  const Smem L = smem_map(p.bm);
+  uint64_t* full_x = reinterpret_cast<uint64_t*>(smem + L.bars);
+  uint64_t* empty_x = full_x + NXS;
+  uint64_t* full_w = empty_x + NXS;
+  uint64_t* empty_w = full_w + NWS;
+  uint64_t* full_a = empty_w + NWS;
+  uint64_t* empty_a = full_a + NAS;
+  uint64_t* full_d = empty_a + NAS;
+  uint64_t* empty_d = full_d + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L.tmem_slot);
+  volatile int* flag_abort = reinterpret_cast<volatile int*>(smem + L.flags);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int x_stage_bytes = p.bm * 128;
+  const int k_tiles = p.K / BK;
+  const int total_tiles = p.n_tiles_n * p.n_tiles_m;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NXS; ++i) { mbar_init(&full_x[i], 1); mbar_init(&empty_x[i], 1); }
+    for (int i = 0; i < NWS; ++i) { mbar_init(&full_w[i], 1); mbar_init(&empty_w[i], N_DQ_WARPS); }
+    for (int i = 0; i < NAS; ++i) { mbar_init(&full_a[i], N_DQ_WARPS); mbar_init(&empty_a[i], 1); }
+    mbar_init(full_d, 1);
+    mbar_init(empty_d, 4);
+    *flag_abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == WARP_MMA) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+#define LCQ_GIVE_UP(code) do { *flag_abort = 1; atomicExch(&g_device_status, (code)); } while (0)
+
+  if (warp == WARP_TMA) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_x); tma_prefetch_desc(&tmap_w); tma_prefetch_desc(&tmap_s);
+      uint32_t xi = 0, wi = 0;   // running stage counters
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / p.n_tiles_n) * p.bm, n0 = (tile % p.n_tiles_n) * BN;
+        for (int kt = 0; kt < k_tiles && ok; ++kt) {
+          if ((kt & 3) == 0) {
+            const uint32_t s = wi % NWS, ph = (wi / NWS) & 1;
+            if (*flag_abort || !mbar_wait_bounded(&empty_w[s], ph ^ 1)) { LCQ_GIVE_UP(10); ok = false; break; }
+            uint8_t* dst = smem + L.w + s * WS_STAGE;
+            mbar_expect_tx(&full_w[s], WS_STAGE);
+            tma_load_2d(dst, &tmap_w, &full_w[s], (kt / 4) * (WK / 2), n0);
+            tma_load_2d(dst + W_STAGE, &tmap_s, &full_w[s], (kt / 4) * (WK / 32), n0);
+            ++wi;
+          }
+          const uint32_t s = xi % NXS, ph = (xi / NXS) & 1;
+          if (*flag_abort || !mbar_wait_bounded(&empty_x[s], ph ^ 1)) { LCQ_GIVE_UP(11); ok = false; break; }
+          mbar_expect_tx(&full_x[s], x_stage_bytes);
+          tma_load_2d(smem + L.x + s * x_stage_bytes, &tmap_x, &full_x[s], kt * BK, m0);
+          ++xi;
+        }
+      }
+    }
+  } else if (warp == WARP_MMA) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(p.bm);
+      uint32_t xi = 0, ai = 0, di = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++di) {
+        if (*flag_abort || !mbar_wait_bounded(empty_d, (di & 1) ^ 1)) { LCQ_GIVE_UP(12); ok = false; break; }
+        tc_fence_after();
+        for (int kt = 0; kt < k_tiles && ok; ++kt, ++xi, ++ai) {
+          const uint32_t sx = xi % NXS, phx = (xi / NXS) & 1;
+          const uint32_t sa = ai % NAS, pha = (ai / NAS) & 1;
+          if (*flag_abort || !mbar_wait_bounded(&full_x[sx], phx) || !mbar_wait_bounded(&full_a[sa], pha)) {
+            LCQ_GIVE_UP(14); ok = false; break;
+          }
+          tc_fence_after();
+          const uint64_t bdesc = make_b_desc(smem_u32(smem + L.x + sx * x_stage_bytes));
+          const uint32_t a_t = tmem_base + A_COL0 + sa * A_SLOT_COLS;
+#pragma unroll
+          for (int j = 0; j < BK / 16; ++j)
+            umma_f16_ts(tmem_base, a_t + j * 8, bdesc + static_cast<uint64_t>(2 * j), idesc, (kt | j) != 0 ? 1u : 0u);
+          umma_commit(&empty_x[sx]);
+          umma_commit(&empty_a[sa]);
+        }
+        if (ok) umma_commit(full_d);
+      }
+    }
+  } else if (warp >= WARP_DQ0) {
+    // ------------------------------------------------------------ dequant warps: smem int4 -> TMEM fp16
+    const int q4 = warp & 3;                    // TMEM lane quarter this warp may touch
+    const int h = (warp - WARP_DQ0) >> 2;       // which 32-wide half of the 64-k tile
+    const int r = q4 * 32 + lane;               // weight row inside the tile = TMEM lane
+    const uint32_t lane_taddr = tmem_base + (static_cast<uint32_t>(q4 * 32) << 16) + A_COL0 + h * 16;
+    uint32_t ai = 0, wi = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int kt = 0; kt < k_tiles && ok; ++kt, ++ai) {
+        const int q = kt & 3;
+        const uint32_t sw = wi % NWS;
+        if (q == 0) {
+          if (!warp_wait(flag_abort, &full_w[sw], (wi / NWS) & 1)) { LCQ_GIVE_UP(15); ok = false; break; }
+        }
+        const uint32_t sa = ai % NAS;
+        if (!warp_wait(flag_abort, &empty_a[sa], ((ai / NAS) & 1) ^ 1)) { LCQ_GIVE_UP(16); ok = false; break; }
+        tc_fence_after();
+        const uint8_t* wst = smem + L.w + sw * WS_STAGE;
+        const int c = q * 2 + h;                // 16-byte chunk (= one 32-wide group) of the 128-byte row
+        const uint4 pk = *reinterpret_cast<const uint4*>(wst + r * 128 + ((c ^ (r & 7)) << 4));
+        const __half sc = *reinterpret_cast<const __half*>(wst + W_STAGE + r * 16 + c * 2);
+        const __half2 s2 = __half2half2(sc);
+        uint32_t v[16];
+        {
+          uint32_t o[4];
+          dequant_word(pk.x, s2, o); v[0] = o[0]; v[1] = o[1]; v[2] = o[2]; v[3] = o[3];
+          dequant_word(pk.y, s2, o); v[4] = o[0]; v[5] = o[1]; v[6] = o[2]; v[7] = o[3];
+          dequant_word(pk.z, s2, o); v[8] = o[0]; v[9] = o[1]; v[10] = o[2]; v[11] = o[3];
+          dequant_word(pk.w, s2, o); v[12] = o[0]; v[13] = o[1]; v[14] = o[2]; v[15] = o[3];
+        }
+        tmem_st16(lane_taddr + sa * A_SLOT_COLS, v);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&full_a[sa]);
+          if (q == 3) mbar_arrive(&empty_w[sw]);
+        }
+        if (q == 3) ++wi;
+      }
+    }
+  } else if (warp < 4) {
+    // ------------------------------------------------------------ epilogue warps: TMEM -> global
+    OT* out = static_cast<OT*>(p.out);
+    uint32_t di = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++di) {
+      const int m0 = (tile / p.n_tiles_n) * p.bm, n0 = (tile % p.n_tiles_n) * BN;
+      if (!warp_wait(flag_abort, full_d, di & 1)) { LCQ_GIVE_UP(17); ok = false; break; }
+      tc_fence_after();
+      const int n = n0 + warp * 32 + lane;
+      for (int cb = 0; cb < p.bm / 32; ++cb) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + cb * 32, v);
+        tmem_wait_ld();
+        if (n < p.N) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int m = m0 + cb * 32 + i;
+            if (m < p.M) out[static_cast<long long>(m) * p.N + n] = from_f32<OT>(__uint_as_float(v[i]));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_d);
+    }
+  }
+#undef LCQ_GIVE_UP
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == WARP_MMA) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// bf16 -> fp16 copy of the activations (exact for |x| in fp16's normal range)
+__global__ void __launch_bounds__(256) bf16_to_f16_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, long long n16) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += stride) {
+    const uint4 a = __ldg(in + i);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __half2 h = __floats2half2_rn(__uint_as_float(w[j] << 16), __uint_as_float(w[j] & 0xFFFF0000u));
+      o[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// ---------------------------------------------------------------------------- host side
+inline bool supported(int M, int N, int K, int G, int x_dtype, int scale_dtype) {
+  return M >= 1 && N >= 1 && K >= WK && (K % WK) == 0 && G == 32 &&
+         (x_dtype == LCQ_F16 || x_dtype == LCQ_BF16) && scale_dtype == LCQ_F16;
+}
+
+inline size_t workspace_bytes(int M, int N, int K, int x_dtype) {
+  (void)N;
+  // the fp16 copy of bf16 activations sits behind the shared counter region and never touches it
+  return x_dtype == LCQ_BF16 ? kWorkspaceCounterBytes + ((static_cast<size_t>(M) * K * 2 + 255) & ~static_cast<size_t>(255)) : 0;
+}
+
+template <typename OT>
+int launch_t(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& ts, const Params& p, int grid,
+             size_t smem_bytes, cudaStream_t stream) {
+  auto kern = w4a16_gemm_kernel<OT>;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  LCQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    LCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    configured_device = dev;
+  }
+  kern<<<grid, NTHREADS, smem_bytes, stream>>>(tx, tw, ts, p);
+  LCQ_CUDA_TRY(cudaGetLastError());
+  return LCQ_OK;
+}
+
+inline int launch(const void* x, const void* w, const void* s, void* out, int M, int N, int K, int x_dtype,
+                  int out_dtype, void* workspace, size_t ws_bytes, int sm_count, cudaStream_t stream) {
+  if (!aligned(w, 16) || !aligned(s, 16) || !aligned(x, 16)) {
+    set_error("w4a16 gemm: x, w_packed and scales must be 16-byte aligned");
+    return LCQ_ERR_BAD_ARG;
+  }
+  const void* xh = x;
+  if (x_dtype == LCQ_BF16) {
+    const size_t need = workspace_bytes(M, N, K, x_dtype);
+    if (workspace == nullptr || ws_bytes < need || !aligned(workspace, 256)) {
+      set_error("w4a16 gemm: workspace of %zu bytes (256-byte aligned) required for bf16 activations, got %zu", need, ws_bytes);
+      return LCQ_ERR_WORKSPACE;
+    }
+    const long long n16 = static_cast<long long>(M) * K / 8;
+    long long blocks = (n16 + 255) / 256;
+    if (blocks > static_cast<long long>(sm_count) * 8) blocks = static_cast<long long>(sm_count) * 8;
+    uint8_t* scratch = static_cast<uint8_t*>(workspace) + kWorkspaceCounterBytes;
+    bf16_to_f16_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<const uint4*>(x),
+                                                                     reinterpret_cast<uint4*>(scratch), n16);
+    LCQ_CUDA_TRY(cudaGetLastError());
+    xh = scratch;
+  }
+  Params p;
+  memset(&p, 0, sizeof(p));
+  p.out = out; p.M = M; p.N = N; p.K = K;
+  p.bm = M >= 256 ? 256 : ((M + 31) / 32) * 32;
+  p.n_tiles_n = (N + BN - 1) / BN;
+  p.n_tiles_m = (M + p.bm - 1) / p.bm;
+  p.out_dtype = out_dtype;
+  const long long tiles = static_cast<long long>(p.n_tiles_n) * p.n_tiles_m;
+  const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
+  CUtensorMap tx, tw, ts;
+  int rc = encode_tmap_2d(&tx, 1, xh, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
+                          static_cast<uint64_t>(K) * 2, BK, p.bm, 3);
+  if (rc != LCQ_OK) return rc;
+  rc = encode_tmap_2d(&tw, 0, w, static_cast<uint64_t>(K) / 2, static_cast<uint64_t>(N),
+                      static_cast<uint64_t>(K) / 2, WK / 2, BN, 3);
+  if (rc != LCQ_OK) return rc;
+  rc = encode_tmap_2d(&ts, 1, s, static_cast<uint64_t>(K) / 32, static_cast<uint64_t>(N),
+                      static_cast<uint64_t>(K) / 16, WK / 32, BN, 0);
+  if (rc != LCQ_OK) return rc;
+  const size_t smem_bytes = smem_map(p.bm).total;
+  switch (out_dtype) {
+    case LCQ_F32: return launch_t<float>(tx, tw, ts, p, grid, smem_bytes, stream);
+    case LCQ_F16: return launch_t<__half>(tx, tw, ts, p, grid, smem_bytes, stream);
+    case LCQ_BF16: return launch_t<__nv_bfloat16>(tx, tw, ts, p, grid, smem_bytes, stream);
+    default: break;
+  }
+  set_error("w4a16 gemm: bad out_dtype %d", out_dtype);
+  return LCQ_ERR_BAD_ARG;
+}
+
 }  // namespace gemm_tc
 }  // namespace lcq

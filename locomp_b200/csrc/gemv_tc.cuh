@@ -52,7 +52,8 @@ constexpr int BAR_CONSUMERS = 1;             // named barrier id for the consume
 // for every problem: only the counters must be zero on entry (and are zero again on exit);
 // the partials behind them are scratch that successive calls may leave dirty.
 constexpr int MAX_ROW_BLOCKS = 16384;
-constexpr size_t COUNTER_BYTES = static_cast<size_t>(MAX_ROW_BLOCKS) * NCW * sizeof(int);  // one per (row block, 16-row slab)
+constexpr size_t COUNTER_BYTES = kWorkspaceCounterBytes;  // one int per (row block, 16-row slab)
+static_assert(static_cast<size_t>(MAX_ROW_BLOCKS) * NCW * sizeof(int) <= COUNTER_BYTES, "counter region too small");
 
 // Per m-tile-count configuration: M <= 8 runs two CTAs per SM (16 consumer warps hide the
 // shared-memory and MMA latencies), M <= 16 one CTA with a deeper ring.

@@ -225,7 +225,7 @@ static int matmul_entry(int wbits, const void* x, const void* w, const void* s, 
     }
     case LCQ_ALGO_GEMM_TC:
       if (wbits != 4 || !gemm_tc::supported(M, N, K, G, x_dtype, scale_dtype)) {
-        set_error("GEMM_TC needs int4, group_size 32, K %% 64 == 0, f16 scales, f16/bf16 x");
+        set_error("GEMM_TC needs int4, group_size 32, K %% 256 == 0, f16 scales, f16/bf16 x");
         return LCQ_ERR_UNSUPPORTED;
       }
       return gemm_tc::launch(x, w, s, out, M, N, K, x_dtype, out_dtype, workspace, workspace_bytes, di.sm_count, st);
@@ -322,7 +322,7 @@ size_t lcq_matmul_workspace_bytes(int wbits, int M, int N, int K, int group_size
   }
   if (algo == LCQ_ALGO_GEMM_TC) {
     if (wbits != 4 || !gemm_tc::supported(M, N, K, group_size, x_dtype, scale_dtype)) return static_cast<size_t>(-1);
-    return gemm_tc::workspace_bytes(M, N, K);
+    return gemm_tc::workspace_bytes(M, N, K, x_dtype);
   }
   return static_cast<size_t>(-1);
 }
