@@ -112,6 +112,36 @@ int lcq_matmul_select_algo(int wbits, int M, int N, int K, int group_size,
                            int x_dtype, int scale_dtype, int out_dtype);
 
 /*
+ * Decode matmul that allocates nothing.  No counterpart in the reference.
+ *
+ * Same computation and same kernel as lcq_matmul_int4 with LCQ_ALGO_GEMV_TC (M <= 16,
+ * group_size 32, K % 256 == 0, f16 scales, f16/bf16 x), but the split-K scratch is a fixed array
+ * inside the library instead of a caller-provided workspace.  It exists for callers that cannot
+ * obtain device memory at the point of the call: a serving loop whose framework has taken the
+ * whole device into its own pool (so cudaMalloc fails or is forbidden), or a host that must not
+ * make a call that synchronises the device.  This function, and everything under it, calls no
+ * cudaMalloc / cudaFree and no allocating library routine; the caller still passes x, weights,
+ * scales and out.
+ *
+ * Limits and rules
+ *   - The scratch holds lcq_noalloc_scratch_bytes() bytes (8 MiB); every GPU that loads the
+ *     library keeps that much memory until the process exits.  A problem whose plan needs more
+ *     is refused with LCQ_ERR_WORKSPACE (the message says how much) -- use lcq_matmul_int4.
+ *   - The first call on each device looks up the array's device address and sets kernel
+ *     attributes; make that first call before any stream capture.
+ *   - All calls on a device share the one array, which keeps the previous call's contents; each
+ *     call clears the counters it needs (a cudaMemsetAsync on `stream`).  Two calls that overlap
+ *     on the GPU -- different streams, no ordering between them -- race on it and give wrong
+ *     results; order them, or use lcq_matmul_int4 with separate workspaces.
+ */
+int lcq_matmul_int4_noalloc(const void* x, const void* w_packed, const void* scales, void* out,
+                            int M, int N, int K, int group_size,
+                            int x_dtype, int scale_dtype, int out_dtype, void* stream);
+
+/* Size in bytes of the built-in scratch of lcq_matmul_int4_noalloc.  No counterpart in the reference. */
+size_t lcq_noalloc_scratch_bytes(void);
+
+/*
  * Device-side status word.  Kernels that wait on an mbarrier do so with an iteration limit;
  * when a wait gives up the kernel records it here and returns instead of hanging.  Reads the
  * word of the current device (synchronising `stream` first), clears it and returns LCQ_OK or

@@ -378,6 +378,65 @@ int lcq_gemv_tc_plan_check(int M, int N, int K, int sm_count, int* fields) {
   return LCQ_OK;
 }
 
+// ---------------------------------------------------------------- allocation-free decode entry
+// Scratch for lcq_matmul_int4_noalloc: lives in the library image, so every GPU that loads the
+// library holds these bytes until the process exits.  Zero at load time.
+#define LCQ_NOALLOC_SCRATCH_BYTES (8u * 1024u * 1024u)
+static __device__ __align__(256) unsigned char g_noalloc_scratch[LCQ_NOALLOC_SCRATCH_BYTES];
+static void* g_noalloc_ptr[64];          // device address of the array, per device
+static std::mutex g_noalloc_mu;
+
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address; the
+// address a kernel can use has to be asked for, once per device, with that device current.
+static int noalloc_scratch_address(void** out) {
+  int dev = 0;
+  LCQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) { set_error("device index %d out of range", dev); return LCQ_ERR_BAD_ARG; }
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    LCQ_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    if (ptr == nullptr) { set_error("cudaGetSymbolAddress returned a null address"); return LCQ_ERR_CUDA; }
+    g_noalloc_ptr[dev] = ptr;
+  }
+  *out = g_noalloc_ptr[dev];
+  return LCQ_OK;
+}
+
+int lcq_matmul_int4_noalloc(const void* x, const void* w_packed, const void* scales, void* out, int M, int N, int K,
+                            int group_size, int x_dtype, int scale_dtype, int out_dtype, void* stream) {
+  int rc = check_problem(4, M, N, K, group_size);
+  if (rc != LCQ_OK) return rc;
+  if (!dtype_ok(x_dtype) || !dtype_ok(scale_dtype) || !dtype_ok(out_dtype)) { set_error("bad dtype code"); return LCQ_ERR_BAD_ARG; }
+  if (M == 0 || N == 0) return LCQ_OK;
+  if (!x || !w_packed || !scales || !out) { set_error("null pointer argument"); return LCQ_ERR_BAD_ARG; }
+  if (!gemv_tc::supported(M, N, K, group_size, x_dtype, scale_dtype)) {
+    set_error("lcq_matmul_int4_noalloc covers M <= 16, group_size 32, K %% 256 == 0, f16 scales, f16/bf16 x");
+    return LCQ_ERR_UNSUPPORTED;
+  }
+  DevInfo di;
+  rc = current_dev_info(di);
+  if (rc != LCQ_OK) return rc;
+  if (di.major != 10) { set_error("built for sm_100a only; device is sm_%d%d", di.major, di.minor); return LCQ_ERR_UNSUPPORTED; }
+  const gemv_tc::Plan pl = gemv_tc::make_plan(M, N, K, di.sm_count);
+  if (pl.workspace_bytes > LCQ_NOALLOC_SCRATCH_BYTES) {
+    set_error("problem M=%d N=%d K=%d needs %zu bytes of scratch; the built-in scratch holds %u bytes -- "
+              "use lcq_matmul_int4 with a caller-provided workspace", M, N, K, pl.workspace_bytes,
+              LCQ_NOALLOC_SCRATCH_BYTES);
+    return LCQ_ERR_WORKSPACE;
+  }
+  void* scratch = nullptr;
+  rc = noalloc_scratch_address(&scratch);
+  if (rc != LCQ_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the array keeps whatever the previous call (possibly an aborted one) left: the counters must start at zero
+  LCQ_CUDA_TRY(cudaMemsetAsync(scratch, 0, kWorkspaceCounterBytes, st));
+  return gemv_tc::launch(x, w_packed, scales, out, M, N, K, x_dtype, out_dtype, scratch, LCQ_NOALLOC_SCRATCH_BYTES,
+                         di.sm_count, st);
+}
+
+size_t lcq_noalloc_scratch_bytes(void) { return LCQ_NOALLOC_SCRATCH_BYTES; }
+
 int lcq_check_device_status(void* stream) {
   LCQ_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   int v = 0;
