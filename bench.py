@@ -60,47 +60,52 @@ def load_peaks():
 # clocks sampling during the timed region
 # --------------------------------------------------------------------------------------------
 class ClockSampler:
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and clock-event (throttle) reasons of one GPU through NVML from a host
+    thread, every millisecond, between start() and stop().  The timed region of this bench
+    is milliseconds long, so `nvidia-smi -lms` (>= 100 ms per sample) would see nothing."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
-        self.proc = None
+        self.samples = []
+        self.mask = 0
+        self.smax = None
+        self._stop = False
+        self._thread = None
+        self._err = None
+
+    def _run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+            self.smax = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            while not self._stop:
+                self.samples.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                try:
+                    self.mask |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
+                except Exception:
+                    self.mask |= int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                time.sleep(0.001)
+        except Exception as e:   # NVML missing: report it, do not fail the bench
+            self._err = repr(e)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+        import threading
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, smax, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1]))
-                smax.append(float(parts[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        self._stop = True
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        if self._err or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.smax, "samples": 0, "reasons": [self._err or "no samples"]}
+        reasons = sorted(name for bit, name in self.REASONS.items() if self.mask & bit)
+        return {"sm_mhz": statistics.median(self.samples), "sm_min_mhz": min(self.samples), "sm_max_mhz": self.smax,
+                "samples": len(self.samples), "reasons": reasons}
 
 
 # --------------------------------------------------------------------------------------------
@@ -184,6 +189,36 @@ class Call:
         rc = self.lib.lcq_matmul_int4(*self.args, stream_ptr)
         if rc != 0:
             raise RuntimeError(f"lcq_matmul_int4 failed: {self.lib.lcq_last_error().decode()}")
+
+
+def run_profile_shape(args):
+    """A handful of launches of one (K, N, M) problem: the small case an `ncu` capture wants."""
+    import torch
+    from locomp_b200 import _lib
+    lib = _lib.lib()
+    k, n, m = (int(v) for v in args.profile_shape.lower().split("x"))
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    xdt = "bf16" if m > 16 else "f16"
+    nbuf = max(2, min(8, int(300e6 // weight_bytes(k, n)) + 1))
+    calls = [Call(lib, torch, k, n, m, dev, seed=i, x_dtype=xdt) for i in range(nbuf)]
+    ws = torch.zeros(max(calls[0].ws_bytes, 256), dtype=torch.uint8, device=dev)
+    for c in calls:
+        c.bind(ws)
+    sp = torch.cuda.current_stream().cuda_stream
+    for i in range(args.warmup):
+        calls[i % nbuf].launch(sp)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        calls[(args.warmup + i) % nbuf].launch(sp)
+    e1.record()
+    torch.cuda.synchronize()
+    _lib.check(lib.lcq_check_device_status(None))
+    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    print(json.dumps({"profile_shape": {"K": k, "N": n, "M": m}, "us_per_launch": us,
+                      "weight_gbs": weight_bytes(k, n) / us / 1e3, "tflops": 2.0 * m * n * k / us / 1e6}), flush=True)
 
 
 def run_ours(args, rank: int, world: int, local_rank: int):
@@ -348,6 +383,29 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "frac": achieved / peaks["hbm_gbs"], "avg_launch_us": avg_ms * 1e3,
             "algorithmic_bytes_per_launch": weight_bytes(k, n), "traffic": None,
         }
+    if rank == 0 and args.workload == "cfg4":
+        big = [c for calls in sets for c in calls if c.m == ms[-1] and (c.k, c.n) == shapes[1]]
+        durs = []
+        with torch.cuda.stream(stream):
+            for rep in range(3):
+                for c in big:
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(stream)
+                    c.launch(sp)
+                    b.record(stream)
+                    durs.append((a, b))
+        torch.cuda.synchronize()
+        times = [a.elapsed_time(b) for (a, b) in durs][len(big):]
+        avg_ms = sum(times) / len(times)
+        k, n, m = big[0].k, big[0].n, big[0].m
+        achieved = 2.0 * m * n * k / (avg_ms * 1e-3) / 1e12
+        line["roofline"] = {
+            "bound": "tensor", "kernel": f"w4a16_gemm_kernel (+ bf16->f16 pre-pass) M={m} K={k} N={n}",
+            "achieved": achieved, "peak": peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst)",
+            "peak_sustained": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+            "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"], "avg_launch_us": avg_ms * 1e3,
+            "algorithmic_flops_per_launch": 2.0 * m * n * k, "traffic": None,
+        }
     # ---------------------------------------------------------------- end-to-end through the reference-facing call
     if args.workload == "cfg2":
         host_sets = []
@@ -418,6 +476,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg4", "cfg5"])
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--profile-shape", default=None, metavar="KxNxM",
+                    help="run a few launches of one problem and exit (small case for ncu captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -426,6 +486,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.profile_shape:
+        run_profile_shape(args)
         return
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
