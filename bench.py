@@ -75,25 +75,36 @@ class ClockSampler:
         self._stop = False
         self._thread = None
         self._err = None
+        self._nvml = self._handle = None
 
     def _run(self):
         try:
-            import pynvml
-            pynvml.nvmlInit()
-            h = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
-            self.smax = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            pynvml, h = self._nvml, self._handle
             while not self._stop:
                 self.samples.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
                 try:
                     self.mask |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
                 except Exception:
                     self.mask |= int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
-                time.sleep(0.001)
+                time.sleep(0.0005)
         except Exception as e:   # NVML missing: report it, do not fail the bench
+            self._err = repr(e)
+
+    def prepare(self):
+        """NVML set-up (slow, tens of ms): call before the timed region."""
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+            self.smax = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+        except Exception as e:
             self._err = repr(e)
 
     def start(self):
         import threading
+        if self._err:
+            return
         self._thread = threading.Thread(target=self._run, daemon=True)
         self._thread.start()
 
@@ -312,8 +323,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     with torch.cuda.stream(stream):
         for i in range(args.warmup):
             step(i)
-        barrier()
         sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.prepare()
+        barrier()
         if rank == 0:
             sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
