@@ -287,7 +287,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         for ci, c in enumerate(sets[si]):
             c.launch(sp)
             if world > 1:
-                dist.all_gather_into_tensor(gathered[ci], c.out)
+                dist.all_gather_into_tensor(gathered[ci].view(world * c.m, c.n), c.out)
 
     # eager warm-up (also sets kernel attributes before any graph capture)
     with torch.cuda.stream(stream):
@@ -297,16 +297,25 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     _lib.check(lib.lcq_check_device_status(None))
 
     graphs = None
-    if world == 1 and not args.no_graph:
-        graphs = []
-        for si in range(nsets):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                cap = torch.cuda.current_stream().cuda_stream
-                for c in sets[si]:
-                    c.launch(cap)
-            graphs.append(g)
-        torch.cuda.synchronize()
+    graph_note = "eager"
+    if not args.no_graph:
+        try:
+            graphs = []
+            for si in range(nsets):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    cap = torch.cuda.current_stream().cuda_stream
+                    for ci, c in enumerate(sets[si]):
+                        c.launch(cap)
+                        if world > 1:
+                            dist.all_gather_into_tensor(gathered[ci].view(world * c.m, c.n), c.out)
+                graphs.append(g)
+            torch.cuda.synchronize()
+            graph_note = "cuda_graph"
+        except Exception as e:      # e.g. a collective that cannot be captured: time the eager path instead
+            graphs = None
+            graph_note = f"eager (graph capture failed: {type(e).__name__})"
+            torch.cuda.synchronize()
 
     def step(i):
         si = i % nsets
@@ -361,7 +370,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                          "cfg5": "cfg5: column-sharded W4A16 g=32, 70B shapes, M in {1,16,64}"}[args.workload],
             "shapes_KN": shapes, "M": ms, "calls_per_step": len(shapes) * len(ms), "group_size": GROUP,
             "l2_hygiene": f"every call reads its own weights; {nsets} rotating sets of {per_set_bytes / 1e6:.0f} MB",
-            "launch": "cuda_graph" if graphs is not None else "eager",
+            "launch": graph_note,
             "sharding": None if world == 1 else f"N-column shards + NCCL all-gather, {world} ranks",
         },
         "gpu_launches": args.steps * len(shapes) * len(ms),

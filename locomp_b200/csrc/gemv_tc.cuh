@@ -77,7 +77,6 @@ struct Params {
   int nst;              // K / 256
   int ctas_per_kr;      // CTAs working on one k-range
   int max_split;        // scratch slots per (row block, k-range)
-  int debug_mode;       // EXPERIMENT: 1 = consumers skip the math, 2 = no loads / no waits
 };
 
 struct Sched {          // the share of one k-range's tile sequence owned by one CTA
@@ -166,11 +165,16 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     for (int s = 0; s < NSTAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], NCW); }
     *flag_abort = 0;
     fence_barrier_init();
+    // Programmatic dependent launch: let the next kernel on the stream become resident as our
+    // CTAs retire.  Its producer warp may then prefetch weights (constants) while we finish;
+    // everything that reads activations or touches out / workspace waits for us below.
+    griddep_launch_dependents();
   }
   __syncthreads();
 
   if (warp == NCW) {
     // ------------------------------------------------------------ producer warp
+    // (weights and scales only: they are not produced by the preceding kernel, so no dependency wait)
     if (lane == 0) {
       tma_prefetch_desc(&tmap_w);
       tma_prefetch_desc(&tmap_s);
@@ -180,7 +184,6 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
       for (long long t = t0; t < t1; ++t, ++it) {
         const int s = it % NSTAGES;
         const uint32_t ph = (it / NSTAGES) & 1;
-        if (p.debug_mode == 2) break;
         if (*flag_abort) break;
         if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1)) {
           *flag_abort = 1; atomicExch(&g_device_status, 1);
@@ -203,6 +206,7 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
 
     // ---- stage this k-range of x: permuted element order, fp16, high-nibble slots / 16;
     //      and the zero-point operands -8 * xsum * 2^-9 as fp16 (high part, residual)
+    griddep_wait();   // x may be the previous kernel's output; out / workspace may still be in its use
     {
       const int oct_per_row = sch.S_kr * (KT / 8);
       const int total = p.M * oct_per_row;
@@ -304,12 +308,12 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     uint32_t ph = 0;
     for (int ti = 0; ti < n_tiles; ++ti) {
       const long long t = t0 + ti;
-      if (!dead && p.debug_mode != 2) {
+      if (!dead) {
         if (*flag_abort || !mbar_wait_bounded(&full_bar[s], ph)) {
           dead = true; *flag_abort = 1; atomicExch(&g_device_status, 2);
         }
       }
-      if (!dead && p.debug_mode != 1) {
+      if (!dead) {
         const uint8_t* ws = smem + s * STAGE_BYTES;
         const uint32_t* srA = reinterpret_cast<const uint32_t*>(ws + W_BYTES + r0 * 16);
         const uint32_t* srB = reinterpret_cast<const uint32_t*>(ws + W_BYTES + (r0 + 8) * 16);
@@ -362,8 +366,6 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[s]);  // also in the dead state, so the producer never stalls on us
-      const int s_used = s;
-      (void)s_used;
       if (++s == NSTAGES) { s = 0; ph ^= 1; }
 
       // ---- end of this CTA's share of row block rb: flush.  Each warp settles its own
@@ -506,8 +508,14 @@ inline Plan make_plan(int M, int N, int K, int sm_count) {
   return pl;
 }
 
+// Programmatic dependent launch can be switched off with LCQ_NO_PDL=1 (read once).
+inline bool pdl_enabled() {
+  static const bool on = [] { const char* e = getenv("LCQ_NO_PDL"); return !(e && e[0] == '1'); }();
+  return on;
+}
+
 template <int MT, int NC, typename OT>
-int launch_t(const Plan& pl, const CUtensorMap& tw, const CUtensorMap& ts, cudaStream_t stream) {
+int launch_t(const Plan& pl, const CUtensorMap& tw, const CUtensorMap& ts, bool allow_pdl, cudaStream_t stream) {
   auto kern = w4a16_gemv_kernel<MT, NC, OT>;
   static thread_local int configured_device = -1;  // per (thread, template instance)
   int dev = 0;
@@ -519,20 +527,31 @@ int launch_t(const Plan& pl, const CUtensorMap& tw, const CUtensorMap& ts, cudaS
                                       cudaSharedmemCarveoutMaxShared));
     configured_device = dev;
   }
-  kern<<<pl.grid, NTHREADS, pl.smem_bytes, stream>>>(tw, ts, pl.p);
-  LCQ_CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(pl.grid);
+  cfg.blockDim = dim3(NTHREADS);
+  cfg.dynamicSmemBytes = pl.smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (allow_pdl && pdl_enabled()) ? 1 : 0;
+  LCQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tw, ts, pl.p));
   return LCQ_OK;
 }
 
 template <typename OT>
-int launch_o(const Plan& pl, const CUtensorMap& tw, const CUtensorMap& ts, cudaStream_t stream) {
-  if (pl.MT == 2) return launch_t<2, 2, OT>(pl, tw, ts, stream);
-  if (pl.p.M == 1) return launch_t<1, 1, OT>(pl, tw, ts, stream);
-  return launch_t<1, 2, OT>(pl, tw, ts, stream);
+int launch_o(const Plan& pl, const CUtensorMap& tw, const CUtensorMap& ts, bool allow_pdl, cudaStream_t stream) {
+  if (pl.MT == 2) return launch_t<2, 2, OT>(pl, tw, ts, allow_pdl, stream);
+  if (pl.p.M == 1) return launch_t<1, 1, OT>(pl, tw, ts, allow_pdl, stream);
+  return launch_t<1, 2, OT>(pl, tw, ts, allow_pdl, stream);
 }
 
 inline int launch(const void* x, const void* w, const void* s, void* out, int M, int N, int K, int x_dtype,
-                  int out_dtype, void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream) {
+                  int out_dtype, void* workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream,
+                  bool allow_pdl = true) {
   Plan pl = make_plan(M, N, K, sm_count);
   if (workspace == nullptr || workspace_bytes < pl.workspace_bytes || !aligned(workspace, 256)) {
     set_error("w4a16 gemv: workspace of %zu bytes (256-byte aligned) required, got %zu", pl.workspace_bytes,
@@ -546,7 +565,6 @@ inline int launch(const void* x, const void* w, const void* s, void* out, int M,
   pl.p.x = x;
   pl.p.out = out;
   pl.p.x_is_bf16 = (x_dtype == LCQ_BF16);
-  { const char* e = getenv("LCQ_GEMV_DEBUG_MODE"); pl.p.debug_mode = e ? atoi(e) : 0; }
   pl.p.counters = static_cast<int*>(workspace);
   pl.p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + pl.counters_bytes);
   CUtensorMap tw, ts;
@@ -557,9 +575,9 @@ inline int launch(const void* x, const void* w, const void* s, void* out, int M,
                       static_cast<uint64_t>(K) / 16, GT, ROWS, 0);
   if (rc != LCQ_OK) return rc;
   switch (out_dtype) {
-    case LCQ_F32: return launch_o<float>(pl, tw, ts, stream);
-    case LCQ_F16: return launch_o<__half>(pl, tw, ts, stream);
-    case LCQ_BF16: return launch_o<__nv_bfloat16>(pl, tw, ts, stream);
+    case LCQ_F32: return launch_o<float>(pl, tw, ts, allow_pdl, stream);
+    case LCQ_F16: return launch_o<__half>(pl, tw, ts, allow_pdl, stream);
+    case LCQ_BF16: return launch_o<__nv_bfloat16>(pl, tw, ts, allow_pdl, stream);
     default: break;
   }
   set_error("w4a16 gemv: bad out_dtype %d", out_dtype);

@@ -431,8 +431,9 @@ int lcq_matmul_int4_noalloc(const void* x, const void* w_packed, const void* sca
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // the array keeps whatever the previous call (possibly an aborted one) left: the counters must start at zero
   LCQ_CUDA_TRY(cudaMemsetAsync(scratch, 0, kWorkspaceCounterBytes, st));
+  // no programmatic overlap here: the kernel must not start before the memset above has finished
   return gemv_tc::launch(x, w_packed, scales, out, M, N, K, x_dtype, out_dtype, scratch, LCQ_NOALLOC_SCRATCH_BYTES,
-                         di.sm_count, st);
+                         di.sm_count, st, /*allow_pdl=*/false);
 }
 
 size_t lcq_noalloc_scratch_bytes(void) { return LCQ_NOALLOC_SCRATCH_BYTES; }
