@@ -37,6 +37,10 @@ CFG2_SHAPES = [(2048, 2048), (2048, 8192), (8192, 2048), (2048, 49152)]   # (K, 
 CFG2_MS = [1, 4, 16]
 CFG4_SHAPES = [(4096, 4096), (4096, 14336), (14336, 4096)]
 CFG4_MS = [512, 2048, 8192]
+# cfg3: one decode step of a 30-layer SmolLM2-135M-shaped stack, quantized linears only: (K, N) per
+# layer in call order q, k, v, o, gate, up, down, then the lm_head (examples/54_smollm2_inference.py:503-574)
+CFG3_LAYER = [(576, 576), (576, 192), (576, 192), (576, 576), (576, 1536), (576, 1536), (1536, 576)]
+CFG3_LM_HEAD = (576, 49152)
 CFG5_SHAPES = [(8192, 28672), (28672, 8192), (8192, 128256)]
 CFG5_MS = [1, 16, 64]
 GROUP = 32
@@ -250,6 +254,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     if args.workload == "cfg2":
         shapes, ms, xdt = CFG2_SHAPES, CFG2_MS, "f16"
+    elif args.workload == "cfg3":
+        shapes, ms, xdt = CFG3_LAYER * 30 + [CFG3_LM_HEAD], [1], "f16"
     elif args.workload == "cfg4":
         shapes, ms, xdt = CFG4_SHAPES, CFG4_MS, "bf16"
     else:
@@ -366,9 +372,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "dtype": "f16" if xdt == "f16" else "bf16", "data": "synthetic",
         "config": {
             "workload": {"cfg2": "cfg2: W4A16 g=32 GEMV sweep, M in {1,4,16} x SmolLM2-1.7B shapes (K,N)",
+                         "cfg3": "cfg3: decode step of a 30-layer SmolLM2-135M-shaped stack, 211 W4A16 g=32 linears at M=1",
                          "cfg4": "cfg4: W4A16 g=32 prefill GEMM, M in {512,2048,8192} x Llama-3-8B shapes",
                          "cfg5": "cfg5: column-sharded W4A16 g=32, 70B shapes, M in {1,16,64}"}[args.workload],
-            "shapes_KN": shapes, "M": ms, "calls_per_step": len(shapes) * len(ms), "group_size": GROUP,
+            "shapes_KN": shapes if len(shapes) <= 16 else "30 x " + str(CFG3_LAYER) + " + " + str(CFG3_LM_HEAD), "M": ms, "calls_per_step": len(shapes) * len(ms), "group_size": GROUP,
             "l2_hygiene": f"every call reads its own weights; {nsets} rotating sets of {per_set_bytes / 1e6:.0f} MB",
             "launch": graph_note,
             "sharding": None if world == 1 else f"N-column shards + NCCL all-gather, {world} ranks",
@@ -376,11 +383,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "gpu_launches": args.steps * len(shapes) * len(ms),
         "weight_bytes_per_step": per_set_bytes * world,
     }
+    if args.workload == "cfg3":
+        line["us_per_token"] = ms_total / args.steps * 1e3
     if rank == 0:
         line["clocks"] = clocks
     # ---------------------------------------------------------------- roofline of the dominant kernel
     if rank == 0 and args.workload != "cfg4":
-        big = [c for calls in sets for c in calls if c.m == ms[0] and (c.k, c.n) == (shapes[-1][0], local_n(shapes[-1][1]))]
+        big = [calls[-1 if args.workload == "cfg3" else (len(shapes) - 1) * len(ms)] for calls in sets]
         durs = []
         with torch.cuda.stream(stream):
             for rep in range(6):
@@ -398,9 +407,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         times = [a.elapsed_time(b) for (a, b) in durs][len(big):]
         avg_ms = sum(times) / len(times)
         k, n = big[0].k, big[0].n
+        algo = lib.lcq_matmul_select_algo(4, big[0].m, n, k, GROUP, big[0].code, _lib.F16, big[0].code)
+        kname = {_lib.ALGO_SIMT: "gemv_simt_kernel", _lib.ALGO_GEMV_TC: "w4a16_gemv_kernel",
+                 _lib.ALGO_GEMM_TC: "w4a16_gemm_kernel"}.get(algo, "?")
         achieved = weight_bytes(k, n) / (avg_ms * 1e-3) / 1e9
         line["roofline"] = {
-            "bound": "hbm", "kernel": f"w4a16_gemv_kernel M={ms[0]} K={k} N={n}", "achieved": achieved,
+            "bound": "hbm", "kernel": f"{kname} M={big[0].m} K={k} N={n}", "achieved": achieved,
             "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
             "frac": achieved / peaks["hbm_gbs"], "avg_launch_us": avg_ms * 1e3,
             "algorithmic_bytes_per_launch": weight_bytes(k, n), "traffic": None,
@@ -496,7 +508,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg4", "cfg5"])
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--profile-shape", default=None, metavar="KxNxM",
                     help="run a few launches of one problem and exit (small case for ncu captures)")

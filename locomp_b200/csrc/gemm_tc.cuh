@@ -37,8 +37,10 @@ constexpr int NAS = 4;                  // TMEM A slots
 constexpr int A_COL0 = 256;             // first TMEM column of the A ring
 constexpr int A_SLOT_COLS = 32;
 constexpr int TMEM_COLS = 512;
-constexpr int NTHREADS = 512;
-constexpr int WARP_TMA = 4, WARP_MMA = 5, WARP_DQ0 = 8, N_DQ_WARPS = 8;
+constexpr int WARP_TMA = 4, WARP_MMA = 5, WARP_DQ0 = 8;
+constexpr int N_DQ_WARPS = 8;                 // 8 or 16 (16: two sets of warps take alternate 64-k tiles)
+constexpr int DQ_PAR = N_DQ_WARPS / 8;
+constexpr int NTHREADS = (WARP_DQ0 + N_DQ_WARPS) * 32;
 
 // ---------------------------------------------------------------- tcgen05 wrappers
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -101,6 +103,7 @@ struct Params {
   int bm;               // activation rows per tile (MMA N): multiple of 32, <= 256
   int n_tiles_n, n_tiles_m;
   int out_dtype;
+  int vec_store;        // N and out allow 16-byte stores
 };
 
 struct Smem {           // offsets from the 1024-byte aligned dynamic shared memory base
@@ -109,6 +112,7 @@ struct Smem {           // offsets from the 1024-byte aligned dynamic shared mem
   int bars;
   int tmem_slot;
   int flags;
+  int stage;            // epilogue staging: 2 x [32 m][128 n] of the output type (sized for float)
   int total;
 };
 __host__ __device__ inline Smem smem_map(int bm) {
@@ -119,11 +123,15 @@ __host__ __device__ inline Smem smem_map(int bm) {
   // full_x, empty_x [NXS]; full_w, empty_w [NWS]; full_a, empty_a [NAS]; full_d, empty_d
   s.tmem_slot = s.bars + (2 * NXS + 2 * NWS + 2 * NAS + 2) * 8;
   s.flags = s.tmem_slot + 8;
-  s.total = s.flags + 8;
+  s.stage = (s.flags + 8 + 15) & ~15;
+  s.total = s.stage + 2 * 32 * BN * 4;
   return s;
 }
 
 // RN((q - 8) * s) for the 8 nibbles of a word, as 4 half2 in natural k order.
+// PERM = true leaves them in the order the masks deliver -- (e0,e4) (e1,e5) (e2,e6) (e3,e7) --
+// for activations whose k order was permuted the same way by the pre-pass (saves 4 PRMT).
+template <bool PERM>
 __device__ __forceinline__ void dequant_word(uint32_t w, __half2 s2, uint32_t (&o)[4]) {
   const __half2 k1032 = __half2half2(__ushort_as_half(0x6408));   // 1032.0
   const __half2 k16th = __half2half2(__ushort_as_half(0x2C00));   // 1/16
@@ -140,10 +148,14 @@ __device__ __forceinline__ void dequant_word(uint32_t w, __half2 s2, uint32_t (&
   p0 = __hmul2(p0, s2); p1 = __hmul2(p1, s2); p2 = __hmul2(p2, s2); p3 = __hmul2(p3, s2);
   const uint32_t u0 = *reinterpret_cast<uint32_t*>(&p0), u1 = *reinterpret_cast<uint32_t*>(&p1);
   const uint32_t u2 = *reinterpret_cast<uint32_t*>(&p2), u3 = *reinterpret_cast<uint32_t*>(&p3);
-  o[0] = __byte_perm(u0, u1, 0x5410);   // (e0, e1)
-  o[1] = __byte_perm(u2, u3, 0x5410);   // (e2, e3)
-  o[2] = __byte_perm(u0, u1, 0x7632);   // (e4, e5)
-  o[3] = __byte_perm(u2, u3, 0x7632);   // (e6, e7)
+  if (PERM) {
+    o[0] = u0; o[1] = u1; o[2] = u2; o[3] = u3;
+  } else {
+    o[0] = __byte_perm(u0, u1, 0x5410);   // (e0, e1)
+    o[1] = __byte_perm(u2, u3, 0x5410);   // (e2, e3)
+    o[2] = __byte_perm(u0, u1, 0x7632);   // (e4, e5)
+    o[3] = __byte_perm(u2, u3, 0x7632);   // (e6, e7)
+  }
 }
 
 // Bounded wait whose verdict is the same in every lane, so warp-aligned instructions that
@@ -153,7 +165,7 @@ __device__ __forceinline__ bool warp_wait(volatile int* flag_abort, uint64_t* ba
   return __all_sync(0xffffffffu, ok);
 }
 
-template <typename OT>
+template <typename OT, bool PERM>
 __global__ void __launch_bounds__(NTHREADS, 1)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                   const __grid_constant__ CUtensorMap tmap_s, const Params p) {
@@ -182,7 +194,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
   if (threadIdx.x == 0) {
     for (int i = 0; i < NXS; ++i) { mbar_init(&full_x[i], 1); mbar_init(&empty_x[i], 1); }
     for (int i = 0; i < NWS; ++i) { mbar_init(&full_w[i], 1); mbar_init(&empty_w[i], N_DQ_WARPS); }
-    for (int i = 0; i < NAS; ++i) { mbar_init(&full_a[i], N_DQ_WARPS); mbar_init(&empty_a[i], 1); }
+    for (int i = 0; i < NAS; ++i) { mbar_init(&full_a[i], 8); mbar_init(&empty_a[i], 1); }
     mbar_init(full_d, 1);
     mbar_init(empty_d, 4);
     *flag_abort = 0;
@@ -251,71 +263,111 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     }
   } else if (warp >= WARP_DQ0) {
     // ------------------------------------------------------------ dequant warps: smem int4 -> TMEM fp16
+    // Thread = weight row = TMEM lane; warpgroup bit 0 picks the 32-wide half of a 64-k tile.  With
+    // 16 warps the second pair of warpgroups takes the odd tiles (DQ_PAR = 2).  Software-pipelined
+    // by one tile: the registers of a warp's next tile are computed while the tcgen05.st of its
+    // current one is in flight; only then is that store waited for and the slot handed to the MMA.
     const int q4 = warp & 3;                    // TMEM lane quarter this warp may touch
-    const int h = (warp - WARP_DQ0) >> 2;       // which 32-wide half of the 64-k tile
+    const int wg = (warp - WARP_DQ0) >> 2;      // 0..3
+    const int h = wg & 1;                       // which 32-wide half of the 64-k tile
+    const int par = wg >> 1;                    // which tiles: kt % 2 == par
     const int r = q4 * 32 + lane;               // weight row inside the tile = TMEM lane
     const uint32_t lane_taddr = tmem_base + (static_cast<uint32_t>(q4 * 32) << 16) + A_COL0 + h * 16;
-    uint32_t ai = 0, wi = 0;
+    const int my_tiles = (total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+    const long long n_steps = static_cast<long long>(my_tiles) * k_tiles;   // 64-k tiles this CTA processes (even)
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      for (int kt = 0; kt < k_tiles && ok; ++kt, ++ai) {
-        const int q = kt & 3;
-        const uint32_t sw = wi % NWS;
-        if (q == 0) {
-          if (!warp_wait(flag_abort, &full_w[sw], (wi / NWS) & 1)) { LCQ_GIVE_UP(15); ok = false; break; }
-        }
-        const uint32_t sa = ai % NAS;
-        if (!warp_wait(flag_abort, &empty_a[sa], ((ai / NAS) & 1) ^ 1)) { LCQ_GIVE_UP(16); ok = false; break; }
-        tc_fence_after();
-        const uint8_t* wst = smem + L.w + sw * WS_STAGE;
-        const int c = q * 2 + h;                // 16-byte chunk (= one 32-wide group) of the 128-byte row
-        const uint4 pk = *reinterpret_cast<const uint4*>(wst + r * 128 + ((c ^ (r & 7)) << 4));
-        const __half sc = *reinterpret_cast<const __half*>(wst + W_STAGE + r * 16 + c * 2);
-        const __half2 s2 = __half2half2(sc);
-        uint32_t v[16];
-        {
-          uint32_t o[4];
-          dequant_word(pk.x, s2, o); v[0] = o[0]; v[1] = o[1]; v[2] = o[2]; v[3] = o[3];
-          dequant_word(pk.y, s2, o); v[4] = o[0]; v[5] = o[1]; v[6] = o[2]; v[7] = o[3];
-          dequant_word(pk.z, s2, o); v[8] = o[0]; v[9] = o[1]; v[10] = o[2]; v[11] = o[3];
-          dequant_word(pk.w, s2, o); v[12] = o[0]; v[13] = o[1]; v[14] = o[2]; v[15] = o[3];
-        }
-        tmem_st16(lane_taddr + sa * A_SLOT_COLS, v);
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&full_a[sa]);
-          if (q == 3) mbar_arrive(&empty_w[sw]);
-        }
-        if (q == 3) ++wi;
+    uint32_t v[16];
+
+    // registers of step `st` (packed tile q = st % 4 of weight stage st / 4)
+    auto produce = [&](long long st) -> bool {
+      const int q = static_cast<int>(st & 3);
+      const uint32_t wi = static_cast<uint32_t>(st >> 2);
+      const uint32_t sw = wi % NWS;
+      if (q < DQ_PAR) {                         // this warp's first tile in the weight stage
+        if (!warp_wait(flag_abort, &full_w[sw], (wi / NWS) & 1)) return false;
       }
+      const uint8_t* wst = smem + L.w + sw * WS_STAGE;
+      const int c = q * 2 + h;                  // 16-byte chunk (= one 32-wide group) of the 128-byte row
+      const uint4 pk = *reinterpret_cast<const uint4*>(wst + r * 128 + ((c ^ (r & 7)) << 4));
+      const __half2 s2 = __half2half2(*reinterpret_cast<const __half*>(wst + W_STAGE + r * 16 + c * 2));
+      uint32_t o[4];
+      dequant_word<PERM>(pk.x, s2, o); v[0] = o[0]; v[1] = o[1]; v[2] = o[2]; v[3] = o[3];
+      dequant_word<PERM>(pk.y, s2, o); v[4] = o[0]; v[5] = o[1]; v[6] = o[2]; v[7] = o[3];
+      dequant_word<PERM>(pk.z, s2, o); v[8] = o[0]; v[9] = o[1]; v[10] = o[2]; v[11] = o[3];
+      dequant_word<PERM>(pk.w, s2, o); v[12] = o[0]; v[13] = o[1]; v[14] = o[2]; v[15] = o[3];
+      __syncwarp();
+      if (q >= 4 - DQ_PAR && lane == 0) mbar_arrive(&empty_w[sw]);   // this warp's last read of the weight stage
+      return true;
+    };
+
+    if (n_steps > par && !produce(par)) { LCQ_GIVE_UP(15); ok = false; }
+    for (long long st = par; st < n_steps && ok; st += DQ_PAR) {
+      const uint32_t ai = static_cast<uint32_t>(st);
+      const uint32_t sa = ai % NAS;
+      if (!warp_wait(flag_abort, &empty_a[sa], ((ai / NAS) & 1) ^ 1)) { LCQ_GIVE_UP(16); ok = false; break; }
+      tc_fence_after();
+      tmem_st16(lane_taddr + sa * A_SLOT_COLS, v);         // registers are read at issue
+      if (st + DQ_PAR < n_steps) {
+        if (!produce(st + DQ_PAR)) { LCQ_GIVE_UP(15); ok = false; }   // overlaps the store in flight
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full_a[sa]);
     }
   } else if (warp < 4) {
-    // ------------------------------------------------------------ epilogue warps: TMEM -> global
+    // ------------------------------------------------------------ epilogue warps: TMEM -> smem -> global
+    // The accumulator is n-major (lane = n, column = m) while out is [M, N]: 32 columns at a
+    // time are converted and transposed through a double-buffered staging tile [32 m][128 n],
+    // then written with 16-byte stores, 256 contiguous bytes (128 n) per output row.
     OT* out = static_cast<OT*>(p.out);
-    uint32_t di = 0;
+    OT* stage = reinterpret_cast<OT*>(smem + L.stage);
+    constexpr int VEC = 16 / sizeof(OT);                 // outputs per 16-byte store
+    constexpr int ROW_VECS = BN / VEC;                   // 16-byte pieces per staged row
+    const int et = warp * 32 + lane;                     // 0..127
+    uint32_t di = 0, chunk = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++di) {
       const int m0 = (tile / p.n_tiles_n) * p.bm, n0 = (tile % p.n_tiles_n) * BN;
       if (!warp_wait(flag_abort, full_d, di & 1)) { LCQ_GIVE_UP(17); ok = false; break; }
       tc_fence_after();
-      const int n = n0 + warp * 32 + lane;
-      for (int cb = 0; cb < p.bm / 32; ++cb) {
+      const int n_cb = p.bm / 32;
+      for (int cb = 0; cb < n_cb; ++cb, ++chunk) {
         uint32_t v[32];
         tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + cb * 32, v);
         tmem_wait_ld();
-        if (n < p.N) {
+        if (cb == n_cb - 1) {                            // accumulator fully read: the next tile's MMAs may start
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(empty_d);
+        }
+        OT* sb = stage + (chunk & 1) * (32 * BN);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int m = m0 + cb * 32 + i;
-            if (m < p.M) out[static_cast<long long>(m) * p.N + n] = from_f32<OT>(__uint_as_float(v[i]));
+        for (int i = 0; i < 32; ++i) sb[i * BN + et] = from_f32<OT>(__uint_as_float(v[i]));
+        named_bar_sync(2, 128);
+        {
+          if (p.vec_store) {
+#pragma unroll
+            for (int j = 0; j < (32 * ROW_VECS) / 128; ++j) {
+              const int idx = j * 128 + et;
+              const int mi = idx / ROW_VECS, cv = idx - mi * ROW_VECS;
+              const int m = m0 + cb * 32 + mi, n = n0 + cv * VEC;
+              if (m < p.M && n < p.N) {
+                const uint4 val = *reinterpret_cast<const uint4*>(sb + mi * BN + cv * VEC);
+                *reinterpret_cast<uint4*>(out + static_cast<long long>(m) * p.N + n) = val;
+              }
+            }
+          } else {
+            const int n = n0 + et;
+            if (n < p.N) {
+              for (int i = 0; i < 32; ++i) {
+                const int m = m0 + cb * 32 + i;
+                if (m < p.M) out[static_cast<long long>(m) * p.N + n] = sb[i * BN + et];
+              }
+            }
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty_d);
     }
   }
 #undef LCQ_GIVE_UP
@@ -328,19 +380,21 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
   }
 }
 
-// bf16 -> fp16 copy of the activations (exact for |x| in fp16's normal range)
-__global__ void __launch_bounds__(256) bf16_to_f16_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, long long n16) {
+// bf16 -> fp16 copy of the activations (exact for |x| in fp16's normal range) with the 8 values
+// of every 16-byte piece reordered to (0,4,1,5,2,6,3,7): the order in which the nibble masks
+// deliver the weights, so the dequant warps need no re-pairing.
+__global__ void __launch_bounds__(256) bf16_to_f16_perm_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, long long n16) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += stride) {
     const uint4 a = __ldg(in + i);
     const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-    uint32_t o[4];
+    float f[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const __half2 h = __floats2half2_rn(__uint_as_float(w[j] << 16), __uint_as_float(w[j] & 0xFFFF0000u));
-      o[j] = *reinterpret_cast<const uint32_t*>(&h);
-    }
-    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    for (int j = 0; j < 4; ++j) { f[2 * j] = __uint_as_float(w[j] << 16); f[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u); }
+    const __half2 h0 = __floats2half2_rn(f[0], f[4]), h1 = __floats2half2_rn(f[1], f[5]);
+    const __half2 h2 = __floats2half2_rn(f[2], f[6]), h3 = __floats2half2_rn(f[3], f[7]);
+    out[i] = make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1),
+                        *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
   }
 }
 
@@ -356,15 +410,15 @@ inline size_t workspace_bytes(int M, int N, int K, int x_dtype) {
   return x_dtype == LCQ_BF16 ? kWorkspaceCounterBytes + ((static_cast<size_t>(M) * K * 2 + 255) & ~static_cast<size_t>(255)) : 0;
 }
 
-template <typename OT>
+template <typename OT, bool PERM>
 int launch_t(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& ts, const Params& p, int grid,
              size_t smem_bytes, cudaStream_t stream) {
-  auto kern = w4a16_gemm_kernel<OT>;
+  auto kern = w4a16_gemm_kernel<OT, PERM>;
   static thread_local int configured_device = -1;
   int dev = 0;
   LCQ_CUDA_TRY(cudaGetDevice(&dev));
   if (configured_device != dev) {
-    LCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    LCQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     configured_device = dev;
   }
   kern<<<grid, NTHREADS, smem_bytes, stream>>>(tx, tw, ts, p);
@@ -379,6 +433,8 @@ inline int launch(const void* x, const void* w, const void* s, void* out, int M,
     return LCQ_ERR_BAD_ARG;
   }
   const void* xh = x;
+  // (A mixed fp16 x bf16 MMA was tried in place of this copy: it gave wrong results and a CUDA
+  //  error on B200, so bf16 activations always take the fp16 copy.)
   if (x_dtype == LCQ_BF16) {
     const size_t need = workspace_bytes(M, N, K, x_dtype);
     if (workspace == nullptr || ws_bytes < need || !aligned(workspace, 256)) {
@@ -389,7 +445,7 @@ inline int launch(const void* x, const void* w, const void* s, void* out, int M,
     long long blocks = (n16 + 255) / 256;
     if (blocks > static_cast<long long>(sm_count) * 8) blocks = static_cast<long long>(sm_count) * 8;
     uint8_t* scratch = static_cast<uint8_t*>(workspace) + kWorkspaceCounterBytes;
-    bf16_to_f16_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<const uint4*>(x),
+    bf16_to_f16_perm_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<const uint4*>(x),
                                                                      reinterpret_cast<uint4*>(scratch), n16);
     LCQ_CUDA_TRY(cudaGetLastError());
     xh = scratch;
@@ -397,10 +453,28 @@ inline int launch(const void* x, const void* w, const void* s, void* out, int M,
   Params p;
   memset(&p, 0, sizeof(p));
   p.out = out; p.M = M; p.N = N; p.K = K;
-  p.bm = M >= 256 ? 256 : ((M + 31) / 32) * 32;
   p.n_tiles_n = (N + BN - 1) / BN;
+  if (M < 256) {
+    p.bm = ((M + 31) / 32) * 32;
+  } else {
+    // 256-row tiles amortise the dequantisation best; 128-row tiles fill the machine better when
+    // there are few tiles.  Pick by (last-wave fill) x (per-tile efficiency).
+    double best = -1.0;
+    for (int bm : {256, 128}) {
+      const long long t = static_cast<long long>(p.n_tiles_n) * ((M + bm - 1) / bm);
+      const long long waves = (t + sm_count - 1) / sm_count;
+      const double fill = static_cast<double>(t) / static_cast<double>(waves * sm_count);
+      const double score = fill * (bm == 256 ? 1.0 : 0.8);
+      if (score > best) { best = score; p.bm = bm; }
+    }
+  }
   p.n_tiles_m = (M + p.bm - 1) / p.bm;
   p.out_dtype = out_dtype;
+  {
+    const int vec = out_dtype == LCQ_F32 ? 4 : 8;
+    p.vec_store = (N % vec == 0) && aligned(out, 16);
+  }
+
   const long long tiles = static_cast<long long>(p.n_tiles_n) * p.n_tiles_m;
   const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
   CUtensorMap tx, tw, ts;
@@ -414,10 +488,14 @@ inline int launch(const void* x, const void* w, const void* s, void* out, int M,
                       static_cast<uint64_t>(K) / 16, WK / 32, BN, 0);
   if (rc != LCQ_OK) return rc;
   const size_t smem_bytes = smem_map(p.bm).total;
+  const bool perm = (x_dtype == LCQ_BF16);   // the pre-pass already permuted k inside every 8-block
   switch (out_dtype) {
-    case LCQ_F32: return launch_t<float>(tx, tw, ts, p, grid, smem_bytes, stream);
-    case LCQ_F16: return launch_t<__half>(tx, tw, ts, p, grid, smem_bytes, stream);
-    case LCQ_BF16: return launch_t<__nv_bfloat16>(tx, tw, ts, p, grid, smem_bytes, stream);
+    case LCQ_F32: return perm ? launch_t<float, true>(tx, tw, ts, p, grid, smem_bytes, stream)
+                              : launch_t<float, false>(tx, tw, ts, p, grid, smem_bytes, stream);
+    case LCQ_F16: return perm ? launch_t<__half, true>(tx, tw, ts, p, grid, smem_bytes, stream)
+                              : launch_t<__half, false>(tx, tw, ts, p, grid, smem_bytes, stream);
+    case LCQ_BF16: return perm ? launch_t<__nv_bfloat16, true>(tx, tw, ts, p, grid, smem_bytes, stream)
+                               : launch_t<__nv_bfloat16, false>(tx, tw, ts, p, grid, smem_bytes, stream);
     default: break;
   }
   set_error("w4a16 gemm: bad out_dtype %d", out_dtype);

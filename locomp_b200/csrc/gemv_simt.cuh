@@ -54,6 +54,7 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(const XT* __restrict__ x
   if (VEC) {
     // K % 8 == 0, G % 8 == 0, all rows 16-byte (x) / 4- or 8-byte (w) aligned.
     const int nchunks = K >> 3;
+#pragma unroll 4
     for (int c = lane; c < nchunks; c += 32) {
       const int k0 = c << 3;
       float wq[8];

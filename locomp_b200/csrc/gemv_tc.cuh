@@ -138,7 +138,6 @@ template <int MT, int NC, typename OT>
 __global__ void __launch_bounds__(NTHREADS, Cfg<MT>::CTAS_PER_SM)
 w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_s,
                   const Params p) {
-  constexpr int MP = 8 * MT;
   constexpr int NSTAGES = Cfg<MT>::NSTAGES;
   // Declared 1024-byte aligned (the 128-byte TMA swizzle needs it) and used directly, so the
   // compiler keeps every access in the shared address space with 32-bit addressing.
