@@ -44,6 +44,9 @@ CFG3_LM_HEAD = (576, 49152)
 CFG5_SHAPES = [(8192, 28672), (28672, 8192), (8192, 128256)]
 CFG5_MS = [1, 16, 64]
 GROUP = 32
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
+# profiles/ (bytes), keyed by (K, N, M)
+TRAFFIC_NCU = {(2048, 49152, 1): 56672768 + 139008}
 
 
 def weight_bytes(k: int, n: int) -> int:
@@ -63,64 +66,77 @@ def load_peaks():
 # --------------------------------------------------------------------------------------------
 # clocks sampling during the timed region
 # --------------------------------------------------------------------------------------------
+_SAMPLER_CHILD = r"""
+import sys, time, json
+import pynvml
+pynvml.nvmlInit()
+h = pynvml.nvmlDeviceGetHandleByIndex(int(sys.argv[1]))
+smax = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+print("ready", flush=True)
+sys.stdin.readline()                      # "go"
+import threading
+stop = []
+threading.Thread(target=lambda: (sys.stdin.readline(), stop.append(1)), daemon=True).start()
+samples, mask = [], 0
+while not stop:
+    samples.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+    try:
+        mask |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
+    except Exception:
+        mask |= int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+    time.sleep(0.0005)
+print(json.dumps({"samples": samples, "mask": mask, "smax": smax}), flush=True)
+"""
+
+
 class ClockSampler:
-    """Samples SM clock and clock-event (throttle) reasons of one GPU through NVML from a host
-    thread, every millisecond, between start() and stop().  The timed region of this bench
-    is milliseconds long, so `nvidia-smi -lms` (>= 100 ms per sample) would see nothing."""
+    """Samples SM clock and clock-event (throttle) reasons of one GPU through NVML about every
+    millisecond between start() and stop().  It runs in a child process: the timed region is a
+    few milliseconds of back-to-back launches during which a thread of this process would
+    hardly get to run, and `nvidia-smi -lms` cannot sample faster than ~100 ms."""
 
     REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
                0x80: "hw_power_brake_slowdown"}
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
-        self.samples = []
-        self.mask = 0
-        self.smax = None
-        self._stop = False
-        self._thread = None
+        self.proc = None
         self._err = None
-        self._nvml = self._handle = None
-
-    def _run(self):
-        try:
-            pynvml, h = self._nvml, self._handle
-            while not self._stop:
-                self.samples.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
-                try:
-                    self.mask |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
-                except Exception:
-                    self.mask |= int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
-                time.sleep(0.0005)
-        except Exception as e:   # NVML missing: report it, do not fail the bench
-            self._err = repr(e)
 
     def prepare(self):
-        """NVML set-up (slow, tens of ms): call before the timed region."""
+        """Start the child and let it set NVML up (slow): call before the timed region."""
         try:
-            import pynvml
-            pynvml.nvmlInit()
-            self._nvml = pynvml
-            self._handle = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
-            self.smax = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+            self.proc = subprocess.Popen([sys.executable, "-c", _SAMPLER_CHILD, str(self.gpu_index)],
+                                         stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                                         text=True)
+            if self.proc.stdout.readline().strip() != "ready":
+                raise RuntimeError("NVML sampler did not start")
         except Exception as e:
             self._err = repr(e)
+            self.proc = None
 
     def start(self):
-        import threading
-        if self._err:
-            return
-        self._thread = threading.Thread(target=self._run, daemon=True)
-        self._thread.start()
+        if self.proc is not None:
+            self.proc.stdin.write("go\n")
+            self.proc.stdin.flush()
 
     def stop(self):
-        self._stop = True
-        if self._thread is not None:
-            self._thread.join(timeout=2)
-        if self._err or not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": self.smax, "samples": 0, "reasons": [self._err or "no samples"]}
-        reasons = sorted(name for bit, name in self.REASONS.items() if self.mask & bit)
-        return {"sm_mhz": statistics.median(self.samples), "sm_min_mhz": min(self.samples), "sm_max_mhz": self.smax,
-                "samples": len(self.samples), "reasons": reasons}
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": [self._err or "sampler not started"]}
+        try:
+            self.proc.stdin.write("stop\n")
+            self.proc.stdin.flush()
+            data = json.loads(self.proc.stdout.readline())
+            self.proc.wait(timeout=5)
+        except Exception as e:
+            self.proc.kill()
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": [repr(e)]}
+        samples = data["samples"]
+        if not samples:
+            return {"sm_mhz": None, "sm_max_mhz": data["smax"], "samples": 0, "reasons": ["no samples"]}
+        reasons = sorted(name for bit, name in self.REASONS.items() if data["mask"] & bit)
+        return {"sm_mhz": statistics.median(samples), "sm_min_mhz": min(samples), "sm_max_mhz": data["smax"],
+                "samples": len(samples), "window": "warm-up steps + timed region", "reasons": reasons}
 
 
 # --------------------------------------------------------------------------------------------
@@ -336,14 +352,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         torch.cuda.synchronize()
 
     with torch.cuda.stream(stream):
-        for i in range(args.warmup):
-            step(i)
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.prepare()
+            sampler.start()      # one NVML query takes milliseconds: sample from the warm-up on, through the timed region
+        for i in range(args.warmup):
+            step(i)
         barrier()
-        if rank == 0:
-            sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for i in range(args.steps):
@@ -389,23 +404,25 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         line["clocks"] = clocks
     # ---------------------------------------------------------------- roofline of the dominant kernel
     if rank == 0 and args.workload != "cfg4":
+        # the dominant kernel: the largest shape of the workload at its smallest M, one call per
+        # weight set.  Average launch duration = CUDA events on the launching stream around R
+        # back-to-back launches over rotating weight buffers (R * bytes >> L2), divided by R.
         big = [calls[-1 if args.workload == "cfg3" else (len(shapes) - 1) * len(ms)] for calls in sets]
-        durs = []
+        others = [c for c in sets[0] if c is not big[0]]
+        reps = max(2, int(np.ceil(400e6 / (weight_bytes(big[0].k, big[0].n) * len(big)))))
         with torch.cuda.stream(stream):
-            for rep in range(6):
+            for c in big:                       # warm
+                c.launch(sp)
+            for c in others:                    # push the big buffers out of L2
+                c.launch(sp)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for rep in range(reps):
                 for c in big:
-                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a.record(stream)
                     c.launch(sp)
-                    b.record(stream)
-                    durs.append((a, b))
-                # other sets' small calls between repeats keep the big buffers out of L2
-                for c in sets[rep % nsets]:
-                    if c not in big:
-                        c.launch(sp)
+            b.record(stream)
         torch.cuda.synchronize()
-        times = [a.elapsed_time(b) for (a, b) in durs][len(big):]
-        avg_ms = sum(times) / len(times)
+        avg_ms = a.elapsed_time(b) / (reps * len(big))
         k, n = big[0].k, big[0].n
         algo = lib.lcq_matmul_select_algo(4, big[0].m, n, k, GROUP, big[0].code, _lib.F16, big[0].code)
         kname = {_lib.ALGO_SIMT: "gemv_simt_kernel", _lib.ALGO_GEMV_TC: "w4a16_gemv_kernel",
@@ -415,7 +432,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "bound": "hbm", "kernel": f"{kname} M={big[0].m} K={k} N={n}", "achieved": achieved,
             "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
             "frac": achieved / peaks["hbm_gbs"], "avg_launch_us": avg_ms * 1e3,
-            "algorithmic_bytes_per_launch": weight_bytes(k, n), "traffic": None,
+            "launches_timed": reps * len(big),
+            "algorithmic_bytes_per_launch": weight_bytes(k, n), "traffic": TRAFFIC_NCU.get((k, n, big[0].m)),
         }
     if rank == 0 and args.workload == "cfg4":
         big = [c for calls in sets for c in calls if c.m == ms[-1] and (c.k, c.n) == shapes[1]]
