@@ -266,9 +266,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         import datetime
         import torch.distributed as dist_mod
         dist = dist_mod
-        # Multi-GPU runs stay on the plainest path: eager launches (no graph capture of collectives),
-        # no programmatic dependent launch next to NCCL kernels, and a short collective timeout so a
-        # stuck rank ends the run instead of holding eight GPUs.
+        # Multi-GPU runs: no programmatic dependent launch next to NCCL kernels, and a short collective
+        # timeout so a stuck rank ends the run instead of holding eight GPUs.
         os.environ["LCQ_NO_PDL"] = "1"
         os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "1")
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
@@ -326,7 +325,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     graphs = None
     graph_note = "eager"
-    if not args.no_graph and (world == 1 or args.graph_collectives):
+    if not args.no_graph:
         try:
             graphs = []
             for si in range(nsets):
@@ -522,8 +521,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
+        # Leave without tearing NCCL down: destroying a communicator that captured CUDA graphs still
+        # reference blocks forever (seen at 2 and 8 ranks).  All ranks have printed / finished here.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
@@ -534,22 +538,21 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--graph-collectives", action="store_true",
-                    help="multi-GPU only: capture kernels + NCCL all-gathers in CUDA graphs (default: eager)")
     ap.add_argument("--watchdog", type=int, default=900, help="abort the process after this many seconds")
     ap.add_argument("--profile-shape", default=None, metavar="KxNxM",
                     help="run a few launches of one problem and exit (small case for ncu captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.watchdog > 0:
-        import signal
+        import threading
 
-        def _give_up(signum, frame):
+        def _give_up():
             sys.stderr.write(f"bench.py: watchdog expired after {args.watchdog} s, aborting\n")
             sys.stderr.flush()
             os._exit(3)
-        signal.signal(signal.SIGALRM, _give_up)
-        signal.alarm(args.watchdog)
+        t = threading.Timer(args.watchdog, _give_up)     # a thread: fires even while the main thread sits in a C call
+        t.daemon = True
+        t.start()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
