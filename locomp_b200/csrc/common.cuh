@@ -34,6 +34,12 @@ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
 // Defined here because the library is one translation unit (no relocatable device code).
 __device__ int g_device_status = 0;
 
+// Programmatic dependent launch can be switched off with LCQ_NO_PDL=1 (read once).
+inline bool pdl_enabled() {
+  static const bool on = [] { const char* e = getenv("LCQ_NO_PDL"); return !(e && e[0] == '1'); }();
+  return on;
+}
+
 // ------------------------------------------------------------------ dtype helpers
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }

@@ -44,6 +44,10 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(const XT* __restrict__ x
   const int lane = threadIdx.x & 31;
   const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int m0 = blockIdx.y * MT;
+  // Programmatic dependent launch: this grid may be scheduled while the previous kernel of the
+  // stream drains; x (possibly that kernel's output) and out are touched only after the wait.
+  griddep_launch_dependents();
+  griddep_wait();
   if (n >= N) return;
   const int ns = K / G;
   const ST* srow = scales + static_cast<long long>(n) * ns;
@@ -130,9 +134,21 @@ int launch_gemv_simt(const void* x, const void* w, const void* s, void* out, int
   OT* op = static_cast<OT*>(out);
   const int rows_per_block = 8;
   const unsigned gx = (N + rows_per_block - 1) / rows_per_block;
-#define LCQ_SIMT_LAUNCH(MT_, VEC_)                                                                    \
-  gemv_simt_kernel<WBITS, XT, ST, OT, MT_, VEC_><<<dim3(gx, (M + MT_ - 1) / MT_), 256, 0, stream>>>( \
-      xp, wp, sp, op, M, N, K, G)
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.blockDim = dim3(256);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+#define LCQ_SIMT_LAUNCH(MT_, VEC_)                                                                   \
+  do {                                                                                               \
+    cfg.gridDim = dim3(gx, (M + MT_ - 1) / MT_);                                                     \
+    LCQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_simt_kernel<WBITS, XT, ST, OT, MT_, VEC_>, xp, wp, sp, \
+                                    op, M, N, K, G));                                                \
+  } while (0)
   if (vec) {
     if (M == 1) LCQ_SIMT_LAUNCH(1, true);
     else if (M == 2) LCQ_SIMT_LAUNCH(2, true);
@@ -142,7 +158,6 @@ int launch_gemv_simt(const void* x, const void* w, const void* s, void* out, int
     else LCQ_SIMT_LAUNCH(4, false);
   }
 #undef LCQ_SIMT_LAUNCH
-  LCQ_CUDA_TRY(cudaGetLastError());
   return LCQ_OK;
 }
 

@@ -507,12 +507,6 @@ inline Plan make_plan(int M, int N, int K, int sm_count) {
   return pl;
 }
 
-// Programmatic dependent launch can be switched off with LCQ_NO_PDL=1 (read once).
-inline bool pdl_enabled() {
-  static const bool on = [] { const char* e = getenv("LCQ_NO_PDL"); return !(e && e[0] == '1'); }();
-  return on;
-}
-
 template <int MT, int NC, typename OT>
 int launch_t(const Plan& pl, const CUtensorMap& tw, const CUtensorMap& ts, bool allow_pdl, cudaStream_t stream) {
   auto kern = w4a16_gemv_kernel<MT, NC, OT>;
