@@ -405,6 +405,23 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     }
     if args.workload == "cfg3":
         line["us_per_token"] = ms_total / args.steps * 1e3
+        if rank == 0 and world == 1:
+            # same weights' worth of work with q|k|v and gate|up fused into one launch each
+            # (121 launches per token); four stacks rotate so a stack's 76 MB is out of L2 on reuse
+            stacks = [L.DecodeStack(fused=True, seed=100 + i) for i in range(4)]
+            for st in stacks:
+                st.capture()
+            torch.cuda.synchronize()
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for i in range(args.warmup):
+                stacks[i % 4].replay()
+            f0.record()
+            for i in range(args.steps):
+                stacks[i % 4].replay()
+            f1.record()
+            torch.cuda.synchronize()
+            line["us_per_token_fused_qkv_gateup"] = f0.elapsed_time(f1) / args.steps * 1e3
+            del stacks
     if rank == 0:
         line["clocks"] = clocks
     # ---------------------------------------------------------------- roofline of the dominant kernel

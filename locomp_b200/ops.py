@@ -49,12 +49,16 @@ def _same_device(*ops: Operand) -> int:
 # device-resident forms
 # ------------------------------------------------------------------------------------------
 def quantized_matmul(x, w, scales, group_size: int = 32, *, bits: int = 4, out=None, out_dtype: Optional[str] = None,
-                     algo: Optional[str] = None, stream=None, bf16: bool = False):
+                     algo: Optional[str] = None, stream=None, bf16: bool = False,
+                     workspace_buf: Optional[torch.Tensor] = None):
     """out[m, n] = sum_k x[m, k] * dequant(w)[n, k], float32 accumulation.
 
     x: [K] or [M, K] (f32 / f16 / bf16); w: uint8 [N, K/2] (bits=4) or int8 [N, K] (bits=8);
     scales: [N, K/group_size].  Returns a torch CUDA tensor [N] or [M, N] (or `out`).
     Stream-ordered on `stream` (default: torch's current stream); no host synchronisation.
+    workspace_buf: a zero-initialised uint8 CUDA tensor to use as scratch instead of the
+    per-stream buffer this module keeps (needed under CUDA-graph capture, where nothing may be
+    allocated; see matmul_workspace_bytes).
     """
     xo = resolve(x, "x", bf16)
     wo = resolve(w, "w")
@@ -107,7 +111,12 @@ def quantized_matmul(x, w, scales, group_size: int = 32, *, bits: int = 4, out=N
         ws_bytes = L.lcq_matmul_workspace_bytes(bits, M, N, K, group_size, xk, sk, KIND_TO_CODE[okind], a)
         if ws_bytes == (1 << 64) - 1:
             raise _lib.LcqError(_lib.ERR_UNSUPPORTED, f"algo {algo!r} does not cover this problem")
-        ws = workspace(ws_bytes, dev, sp) if ws_bytes else None
+        if ws_bytes and workspace_buf is not None:
+            if workspace_buf.numel() * workspace_buf.element_size() < ws_bytes or workspace_buf.device.index != dev:
+                raise ValueError(f"workspace_buf must hold {ws_bytes} bytes on cuda:{dev}")
+            ws = workspace_buf
+        else:
+            ws = workspace(ws_bytes, dev, sp) if ws_bytes else None
         fn = L.lcq_matmul_int4 if bits == 4 else L.lcq_matmul_int8
         _lib.check(fn(xo.ptr, wo.ptr, so.ptr, oo.ptr, M, N, K, group_size, xk, sk, KIND_TO_CODE[okind], a,
                       ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, sp))
@@ -118,6 +127,16 @@ def quantized_matmul(x, w, scales, group_size: int = 32, *, bits: int = 4, out=N
     if out is None and squeeze:
         return res[0]
     return res
+
+
+def matmul_workspace_bytes(M: int, N: int, K: int, group_size: int = 32, bits: int = 4, x_kind: str = "f16",
+                           scale_kind: str = "f16", out_kind: Optional[str] = None, algo: Optional[str] = None) -> int:
+    """Scratch bytes quantized_matmul needs for this problem (0 if none)."""
+    n = _lib.lib().lcq_matmul_workspace_bytes(bits, M, N, K, group_size, KIND_TO_CODE[x_kind], KIND_TO_CODE[scale_kind],
+                                              KIND_TO_CODE[out_kind or x_kind], _ALGOS[algo])
+    if n == (1 << 64) - 1:
+        raise ValueError("no kernel covers this problem")
+    return int(n)
 
 
 def dequantize(w, scales, N: Optional[int] = None, K: Optional[int] = None, group_size: int = 32, *, bits: int = 4,

@@ -281,3 +281,36 @@ def test_w4a16_gemm_tc_matches_decode_kernel():
     a = L.quantized_matmul(x, wd, sd, 32, algo="gemv_tc", out_dtype="f32")
     b = L.quantized_matmul(x, wd, sd, 32, algo="gemm_tc", out_dtype="f32")
     torch.testing.assert_close(a, b, rtol=2e-3, atol=2e-2)
+
+
+# --------------------------------------------------------------------------- layers
+def test_fused_projections_equal_separate_ones():
+    rng = np.random.default_rng(21)
+    k = 576
+    parts = [O.make_w4(rng, n, k, 32, np.float16) for n in (576, 192, 192)]
+    dev_parts = [(torch.from_numpy(w).cuda(), torch.from_numpy(s).cuda()) for w, s in parts]
+    x = torch.from_numpy(rng.standard_normal((1, k)).astype(np.float16)).cuda()
+    fused, splits = L.fuse_rows(dev_parts)
+    y = fused(x)
+    assert tuple(y.shape) == (1, 960) and splits == [(0, 576), (576, 768), (768, 960)]
+    for (w, s), (a, b), (wn, sn) in zip(dev_parts, splits, parts):
+        sep = L.QuantLinear(w, s)(x)
+        assert torch.equal(y[:, a:b], sep)                       # rows are independent: bit-identical
+        _check16(sep.float().cpu().numpy(), O.matmul_int4(x.float().cpu().numpy(), wn, sn, 32))
+
+
+def test_decode_stack_counts_and_graph():
+    st = L.DecodeStack(layers=2, fused=False)
+    assert len(st.calls) == 2 * 7 + 1 and st.calls[-1][0].out_features == 49152
+    fu = L.DecodeStack(layers=2, fused=True)
+    assert len(fu.calls) == 2 * 4 + 1 and fu.weight_bytes == st.weight_bytes
+    st.step()
+    eager = [c[2].clone() for c in st.calls]
+    st.capture()
+    for c in st.calls:
+        c[2].zero_()
+    st.replay()
+    torch.cuda.synchronize()
+    for a, c in zip(eager, st.calls):
+        assert torch.equal(a, c[2])
+    _device_status_ok()
