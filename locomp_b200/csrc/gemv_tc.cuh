@@ -410,6 +410,40 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
           const long long slot_elems = static_cast<long long>(p.M) * ROWS;
           float* rb_part = p.partials + static_cast<long long>(rb) * p.n_kr * p.max_split * slot_elems;
           float* part = rb_part + slot * slot_elems;
+          int* counter = p.counters + rb * NCW + warp;
+          // Shortcut: if every other contributor has already published its partial, this warp is
+          // the one that completes the slab -- add the others to the values still in registers and
+          // write the output, without publishing (no global round trip at the kernel's tail).
+          int seen = 0;
+          if (lane == 0) seen = *reinterpret_cast<volatile int*>(counter);
+          seen = __shfl_sync(0xffffffffu, seen, 0);
+          if (seen == n_contrib - 1) {
+            __threadfence();
+            OT* out = static_cast<OT*>(p.out);
+#pragma unroll
+            for (int jm = 0; jm < MT; ++jm) {
+#pragma unroll
+              for (int e = 0; e < NC; ++e) {
+                const int m = 8 * jm + 2 * t4 + e;
+                if (m < p.M) {
+                  float sa = 0.0f, sb = 0.0f;      // same slot order as the reducer below: bit-identical result
+                  for (int kk = 0; kk < p.n_kr; ++kk) {
+                    const int cnt = (kk == p.n_kr - 1) ? c_last : c_full;
+                    for (int c = 0; c < cnt; ++c) {
+                      const int os = kk * p.max_split + c;
+                      const float* src = rb_part + os * slot_elems + m * ROWS + r0;
+                      sa += (os == slot) ? y[jm][e] : __ldcg(src);
+                      sb += (os == slot) ? y[jm][2 + e] : __ldcg(src + 8);
+                    }
+                  }
+                  if (nA < p.N) store_out(out, static_cast<long long>(m) * p.N + nA, sa);
+                  if (nB < p.N) store_out(out, static_cast<long long>(m) * p.N + nB, sb);
+                }
+              }
+            }
+            __syncwarp();
+            if (lane == 0) *counter = 0;
+          } else {
 #pragma unroll
           for (int jm = 0; jm < MT; ++jm) {
 #pragma unroll
@@ -424,7 +458,7 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
           __threadfence();
           __syncwarp();
           int last = 0;
-          if (lane == 0) last = (atomicAdd(p.counters + rb * NCW + warp, 1) == n_contrib - 1) ? 1 : 0;
+          if (lane == 0) last = (atomicAdd(counter, 1) == n_contrib - 1) ? 1 : 0;
           last = __shfl_sync(0xffffffffu, last, 0);
           if (last) {
             __threadfence();
@@ -442,6 +476,7 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
             }
             if (lane == 0) p.counters[rb * NCW + warp] = 0;
           }
+          }   // published path
         }
 #pragma unroll
         for (int jm = 0; jm < MT; ++jm) {
