@@ -207,11 +207,20 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     //      and the zero-point operands -8 * xsum * 2^-9 as fp16 (high part, residual)
     griddep_wait();   // x may be the previous kernel's output; out / workspace may still be in its use
     {
-      const int oct_per_row = sch.S_kr * (KT / 8);
+      // Only the k tiles this CTA will actually visit are staged: its tile range starts at tile
+      // ks0 of a row block and wraps around the k-range, so it touches min(n_tiles, S_kr) tiles.
+      const int ks0 = static_cast<int>(t0 % sch.S_kr);
+      const long long span = t1 - t0;
+      const int need_tiles = span < sch.S_kr ? static_cast<int>(span) : sch.S_kr;
+      const int oct_per_row = need_tiles * (KT / 8);
       const int total = p.M * oct_per_row;
       const long long kbase = static_cast<long long>(kr) * p.S * KT;
-      const int zero16 = (L.bars - L.xs) / 16;
-      for (int i = ctid; i < zero16; i += NCW * 32) xs[i] = make_uint4(0u, 0u, 0u, 0u);
+      // zero the zero-point operands (rows m >= M stay zero) and the block of zeros behind xs
+      {
+        uint4* z = reinterpret_cast<uint4*>(smem + L.corr - 64);
+        const int zero16 = (L.bars - (L.corr - 64)) / 16;
+        for (int i = ctid; i < zero16; i += NCW * 32) z[i] = make_uint4(0u, 0u, 0u, 0u);
+      }
       named_bar_sync(BAR_CONSUMERS, NCW * 32);
       constexpr int U = 4;   // independent 16-byte loads in flight per thread
       for (int base = 0; base < total; base += U * NCW * 32) {
@@ -223,7 +232,12 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
           const int idx = base + u * NCW * 32 + ctid;
           ok[u] = idx < total;
           mm[u] = ok[u] ? idx / oct_per_row : 0;
-          oo[u] = ok[u] ? idx - mm[u] * oct_per_row : 0;
+          {
+            const int ol = ok[u] ? idx - mm[u] * oct_per_row : 0;       // octet within the visited tiles
+            int ks = ks0 + (ol >> 5);                                    // 32 octets per 256-k tile
+            if (ks >= sch.S_kr) ks -= sch.S_kr;
+            oo[u] = ks * (KT / 8) + (ol & 31);
+          }
           raw[u] = make_uint4(0u, 0u, 0u, 0u);
           if (ok[u]) {
             const long long off = static_cast<long long>(mm[u]) * p.K + kbase + 8 * oo[u];
