@@ -102,6 +102,8 @@ struct Params {
   int M, N, K;
   int bm;               // activation rows per tile (MMA N): multiple of 32, <= 256
   int n_tiles_n, n_tiles_m;
+  int splits;           // split-K factor (1 = none); with > 1 `out` is float scratch [splits][M][N]
+  int k_tiles_per_split;  // 64-k tiles per split, a multiple of 4
   int out_dtype;
   int vec_store;        // N and out allow 16-byte stores
 };
@@ -188,8 +190,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int x_stage_bytes = p.bm * 128;
-  const int k_tiles = p.K / BK;
-  const int total_tiles = p.n_tiles_n * p.n_tiles_m;
+  // a work item is (output tile, k split); k_tiles counts the 64-k tiles of one item
+  const int k_tiles = p.k_tiles_per_split;
+  const int total_tiles = p.n_tiles_n * p.n_tiles_m * p.splits;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NXS; ++i) { mbar_init(&full_x[i], 1); mbar_init(&empty_x[i], 1); }
@@ -214,7 +217,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       tma_prefetch_desc(&tmap_x); tma_prefetch_desc(&tmap_w); tma_prefetch_desc(&tmap_s);
       uint32_t xi = 0, wi = 0;   // running stage counters
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x) {
+        const int tile = item / p.splits, kt0 = (item % p.splits) * k_tiles;
         const int m0 = (tile / p.n_tiles_n) * p.bm, n0 = (tile % p.n_tiles_n) * BN;
         for (int kt = 0; kt < k_tiles && ok; ++kt) {
           if ((kt & 3) == 0) {
@@ -222,14 +226,14 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             if (*flag_abort || !mbar_wait_bounded(&empty_w[s], ph ^ 1)) { LCQ_GIVE_UP(10); ok = false; break; }
             uint8_t* dst = smem + L.w + s * WS_STAGE;
             mbar_expect_tx(&full_w[s], WS_STAGE);
-            tma_load_2d(dst, &tmap_w, &full_w[s], (kt / 4) * (WK / 2), n0);
-            tma_load_2d(dst + W_STAGE, &tmap_s, &full_w[s], (kt / 4) * (WK / 32), n0);
+            tma_load_2d(dst, &tmap_w, &full_w[s], ((kt0 + kt) / 4) * (WK / 2), n0);
+            tma_load_2d(dst + W_STAGE, &tmap_s, &full_w[s], ((kt0 + kt) / 4) * (WK / 32), n0);
             ++wi;
           }
           const uint32_t s = xi % NXS, ph = (xi / NXS) & 1;
           if (*flag_abort || !mbar_wait_bounded(&empty_x[s], ph ^ 1)) { LCQ_GIVE_UP(11); ok = false; break; }
           mbar_expect_tx(&full_x[s], x_stage_bytes);
-          tma_load_2d(smem + L.x + s * x_stage_bytes, &tmap_x, &full_x[s], kt * BK, m0);
+          tma_load_2d(smem + L.x + s * x_stage_bytes, &tmap_x, &full_x[s], (kt0 + kt) * BK, m0);
           ++xi;
         }
       }
@@ -320,15 +324,17 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     // The accumulator is n-major (lane = n, column = m) while out is [M, N]: 32 columns at a
     // time are converted and transposed through a double-buffered staging tile [32 m][128 n],
     // then written with 16-byte stores, 256 contiguous bytes (128 n) per output row.
-    OT* out = static_cast<OT*>(p.out);
+    OT* out_base = static_cast<OT*>(p.out);
     OT* stage = reinterpret_cast<OT*>(smem + L.stage);
     constexpr int VEC = 16 / sizeof(OT);                 // outputs per 16-byte store
     constexpr int ROW_VECS = BN / VEC;                   // 16-byte pieces per staged row
     const int et = warp * 32 + lane;                     // 0..127
     uint32_t di = 0, chunk = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++di) {
+    for (int item = blockIdx.x; item < total_tiles && ok; item += gridDim.x, ++di) {
+      const int tile = item / p.splits;
       const int m0 = (tile / p.n_tiles_n) * p.bm, n0 = (tile % p.n_tiles_n) * BN;
+      OT* out = out_base + static_cast<long long>(item % p.splits) * p.M * p.N;   // split-K: this split's partial
       if (!warp_wait(flag_abort, full_d, di & 1)) { LCQ_GIVE_UP(17); ok = false; break; }
       tc_fence_after();
       const int n_cb = p.bm / 32;
@@ -398,16 +404,69 @@ __global__ void __launch_bounds__(256) bf16_to_f16_perm_kernel(const uint4* __re
   }
 }
 
+// out[i] = sum over splits of partial[s][i], rounded once to the output type
+template <typename OT>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, OT* __restrict__ out,
+                                                            long long n, int splits) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float acc = 0.0f;
+    for (int s = 0; s < splits; ++s) acc += __ldcs(part + static_cast<long long>(s) * n + i);
+    out[i] = from_f32<OT>(acc);
+  }
+}
+
 // ---------------------------------------------------------------------------- host side
+struct Tiling { int bm, n_tiles_n, n_tiles_m, splits, k_tiles_per_split; };
+
+// Tile shape and split-K factor.  Few output tiles (small M and modest N) would leave most SMs
+// idle, so K is cut into `splits` ranges (multiples of 256 k) whose float partials are summed by
+// a small second kernel.
+inline Tiling choose_tiling(int M, int N, int K, int sm_count) {
+  Tiling t;
+  t.n_tiles_n = (N + BN - 1) / BN;
+  if (M < 256) {
+    t.bm = ((M + 31) / 32) * 32;
+  } else {
+    double best = -1.0;
+    t.bm = 256;
+    for (int bm : {256, 128}) {
+      const long long tiles = static_cast<long long>(t.n_tiles_n) * ((M + bm - 1) / bm);
+      const long long waves = (tiles + sm_count - 1) / sm_count;
+      const double fill = static_cast<double>(tiles) / static_cast<double>(waves * sm_count);
+      const double score = fill * (bm == 256 ? 1.0 : 0.8);
+      if (score > best) { best = score; t.bm = bm; }
+    }
+  }
+  t.n_tiles_m = (M + t.bm - 1) / t.bm;
+  const long long tiles = static_cast<long long>(t.n_tiles_n) * t.n_tiles_m;
+  const int w_stages = K / WK;                       // 256-k weight stages
+  t.splits = 1;
+  if (tiles * 2 <= sm_count && w_stages >= 2) {
+    int s = static_cast<int>(sm_count / tiles);
+    if (s > w_stages) s = w_stages;
+    if (s > 16) s = 16;
+    while (s > 1 && w_stages % s != 0) --s;            // equal ranges only
+    t.splits = s < 1 ? 1 : s;
+  }
+  t.k_tiles_per_split = (w_stages / t.splits) * (WK / BK);
+  return t;
+}
+
 inline bool supported(int M, int N, int K, int G, int x_dtype, int scale_dtype) {
   return M >= 1 && N >= 1 && K >= WK && (K % WK) == 0 && G == 32 &&
          (x_dtype == LCQ_F16 || x_dtype == LCQ_BF16) && scale_dtype == LCQ_F16;
 }
 
-inline size_t workspace_bytes(int M, int N, int K, int x_dtype) {
-  (void)N;
-  // the fp16 copy of bf16 activations sits behind the shared counter region and never touches it
-  return x_dtype == LCQ_BF16 ? kWorkspaceCounterBytes + ((static_cast<size_t>(M) * K * 2 + 255) & ~static_cast<size_t>(255)) : 0;
+inline size_t x_copy_bytes(int M, int K, int x_dtype) {
+  return x_dtype == LCQ_BF16 ? ((static_cast<size_t>(M) * K * 2 + 255) & ~static_cast<size_t>(255)) : 0;
+}
+// [shared counter region][fp16 copy of bf16 activations][split-K float partials]
+inline size_t workspace_bytes(int M, int N, int K, int x_dtype, int sm_count = 148) {
+  const Tiling t = choose_tiling(M, N, K, sm_count);
+  const size_t part = t.splits > 1 ? static_cast<size_t>(t.splits) * M * N * sizeof(float) : 0;
+  const size_t xc = x_copy_bytes(M, K, x_dtype);
+  return (xc + part) ? kWorkspaceCounterBytes + xc + part : 0;
 }
 
 template <typename OT, bool PERM>
@@ -426,57 +485,59 @@ int launch_t(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& ts
   return LCQ_OK;
 }
 
+template <bool PERM>
+int launch_by_out(int out_dtype, const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& ts, const Params& p,
+                  int grid, size_t smem_bytes, cudaStream_t stream) {
+  switch (out_dtype) {
+    case LCQ_F32: return launch_t<float, PERM>(tx, tw, ts, p, grid, smem_bytes, stream);
+    case LCQ_F16: return launch_t<__half, PERM>(tx, tw, ts, p, grid, smem_bytes, stream);
+    case LCQ_BF16: return launch_t<__nv_bfloat16, PERM>(tx, tw, ts, p, grid, smem_bytes, stream);
+    default: break;
+  }
+  set_error("w4a16 gemm: bad out_dtype %d", out_dtype);
+  return LCQ_ERR_BAD_ARG;
+}
+
 inline int launch(const void* x, const void* w, const void* s, void* out, int M, int N, int K, int x_dtype,
                   int out_dtype, void* workspace, size_t ws_bytes, int sm_count, cudaStream_t stream) {
   if (!aligned(w, 16) || !aligned(s, 16) || !aligned(x, 16)) {
     set_error("w4a16 gemm: x, w_packed and scales must be 16-byte aligned");
     return LCQ_ERR_BAD_ARG;
   }
+  const Tiling t = choose_tiling(M, N, K, sm_count);
+  const size_t need = workspace_bytes(M, N, K, x_dtype, sm_count);
+  if (need && (workspace == nullptr || ws_bytes < need || !aligned(workspace, 256))) {
+    set_error("w4a16 gemm: workspace of %zu bytes (256-byte aligned) required, got %zu", need, ws_bytes);
+    return LCQ_ERR_WORKSPACE;
+  }
+  uint8_t* scratch = need ? static_cast<uint8_t*>(workspace) + kWorkspaceCounterBytes : nullptr;
   const void* xh = x;
   // (A mixed fp16 x bf16 MMA was tried in place of this copy: it gave wrong results and a CUDA
   //  error on B200, so bf16 activations always take the fp16 copy.)
   if (x_dtype == LCQ_BF16) {
-    const size_t need = workspace_bytes(M, N, K, x_dtype);
-    if (workspace == nullptr || ws_bytes < need || !aligned(workspace, 256)) {
-      set_error("w4a16 gemm: workspace of %zu bytes (256-byte aligned) required for bf16 activations, got %zu", need, ws_bytes);
-      return LCQ_ERR_WORKSPACE;
-    }
     const long long n16 = static_cast<long long>(M) * K / 8;
     long long blocks = (n16 + 255) / 256;
     if (blocks > static_cast<long long>(sm_count) * 8) blocks = static_cast<long long>(sm_count) * 8;
-    uint8_t* scratch = static_cast<uint8_t*>(workspace) + kWorkspaceCounterBytes;
     bf16_to_f16_perm_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<const uint4*>(x),
-                                                                     reinterpret_cast<uint4*>(scratch), n16);
+                                                                          reinterpret_cast<uint4*>(scratch), n16);
     LCQ_CUDA_TRY(cudaGetLastError());
     xh = scratch;
   }
+  float* partials = reinterpret_cast<float*>(scratch + x_copy_bytes(M, K, x_dtype));
   Params p;
   memset(&p, 0, sizeof(p));
-  p.out = out; p.M = M; p.N = N; p.K = K;
-  p.n_tiles_n = (N + BN - 1) / BN;
-  if (M < 256) {
-    p.bm = ((M + 31) / 32) * 32;
-  } else {
-    // 256-row tiles amortise the dequantisation best; 128-row tiles fill the machine better when
-    // there are few tiles.  Pick by (last-wave fill) x (per-tile efficiency).
-    double best = -1.0;
-    for (int bm : {256, 128}) {
-      const long long t = static_cast<long long>(p.n_tiles_n) * ((M + bm - 1) / bm);
-      const long long waves = (t + sm_count - 1) / sm_count;
-      const double fill = static_cast<double>(t) / static_cast<double>(waves * sm_count);
-      const double score = fill * (bm == 256 ? 1.0 : 0.8);
-      if (score > best) { best = score; p.bm = bm; }
-    }
-  }
-  p.n_tiles_m = (M + p.bm - 1) / p.bm;
-  p.out_dtype = out_dtype;
+  p.M = M; p.N = N; p.K = K;
+  p.bm = t.bm; p.n_tiles_n = t.n_tiles_n; p.n_tiles_m = t.n_tiles_m;
+  p.splits = t.splits; p.k_tiles_per_split = t.k_tiles_per_split;
+  const int kernel_out_dtype = t.splits > 1 ? LCQ_F32 : out_dtype;
+  p.out = t.splits > 1 ? static_cast<void*>(partials) : out;
+  p.out_dtype = kernel_out_dtype;
   {
-    const int vec = out_dtype == LCQ_F32 ? 4 : 8;
-    p.vec_store = (N % vec == 0) && aligned(out, 16);
+    const int vec = kernel_out_dtype == LCQ_F32 ? 4 : 8;
+    p.vec_store = (N % vec == 0) && aligned(p.out, 16) && ((static_cast<long long>(M) * N) % vec == 0);
   }
-
-  const long long tiles = static_cast<long long>(p.n_tiles_n) * p.n_tiles_m;
-  const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
+  const long long items = static_cast<long long>(p.n_tiles_n) * p.n_tiles_m * p.splits;
+  const int grid = static_cast<int>(items < sm_count ? items : sm_count);
   CUtensorMap tx, tw, ts;
   int rc = encode_tmap_2d(&tx, 1, xh, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
                           static_cast<uint64_t>(K) * 2, BK, p.bm, 3);
@@ -489,17 +550,20 @@ inline int launch(const void* x, const void* w, const void* s, void* out, int M,
   if (rc != LCQ_OK) return rc;
   const size_t smem_bytes = smem_map(p.bm).total;
   const bool perm = (x_dtype == LCQ_BF16);   // the pre-pass already permuted k inside every 8-block
+  rc = perm ? launch_by_out<true>(kernel_out_dtype, tx, tw, ts, p, grid, smem_bytes, stream)
+            : launch_by_out<false>(kernel_out_dtype, tx, tw, ts, p, grid, smem_bytes, stream);
+  if (rc != LCQ_OK || t.splits == 1) return rc;
+  const long long n = static_cast<long long>(M) * N;
+  long long blocks = (n + 255) / 256;
+  if (blocks > static_cast<long long>(sm_count) * 8) blocks = static_cast<long long>(sm_count) * 8;
   switch (out_dtype) {
-    case LCQ_F32: return perm ? launch_t<float, true>(tx, tw, ts, p, grid, smem_bytes, stream)
-                              : launch_t<float, false>(tx, tw, ts, p, grid, smem_bytes, stream);
-    case LCQ_F16: return perm ? launch_t<__half, true>(tx, tw, ts, p, grid, smem_bytes, stream)
-                              : launch_t<__half, false>(tx, tw, ts, p, grid, smem_bytes, stream);
-    case LCQ_BF16: return perm ? launch_t<__nv_bfloat16, true>(tx, tw, ts, p, grid, smem_bytes, stream)
-                               : launch_t<__nv_bfloat16, false>(tx, tw, ts, p, grid, smem_bytes, stream);
-    default: break;
+    case LCQ_F32: splitk_reduce_kernel<float><<<static_cast<int>(blocks), 256, 0, stream>>>(partials, static_cast<float*>(out), n, t.splits); break;
+    case LCQ_F16: splitk_reduce_kernel<__half><<<static_cast<int>(blocks), 256, 0, stream>>>(partials, static_cast<__half*>(out), n, t.splits); break;
+    case LCQ_BF16: splitk_reduce_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, stream>>>(partials, static_cast<__nv_bfloat16*>(out), n, t.splits); break;
+    default: set_error("w4a16 gemm: bad out_dtype %d", out_dtype); return LCQ_ERR_BAD_ARG;
   }
-  set_error("w4a16 gemm: bad out_dtype %d", out_dtype);
-  return LCQ_ERR_BAD_ARG;
+  LCQ_CUDA_TRY(cudaGetLastError());
+  return LCQ_OK;
 }
 
 }  // namespace gemm_tc

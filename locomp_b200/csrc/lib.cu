@@ -322,7 +322,7 @@ size_t lcq_matmul_workspace_bytes(int wbits, int M, int N, int K, int group_size
   }
   if (algo == LCQ_ALGO_GEMM_TC) {
     if (wbits != 4 || !gemm_tc::supported(M, N, K, group_size, x_dtype, scale_dtype)) return static_cast<size_t>(-1);
-    return gemm_tc::workspace_bytes(M, N, K, x_dtype);
+    return gemm_tc::workspace_bytes(M, N, K, x_dtype, sm);
   }
   return static_cast<size_t>(-1);
 }

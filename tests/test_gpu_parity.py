@@ -271,6 +271,22 @@ def test_w4a16_gemm_tc_small_shapes(m, n, k, xdt):
     _device_status_ok()
 
 
+def test_w4a16_gemm_tc_split_k_sharded_70b_shape():
+    """M = 64 on one eighth of the (8192, 28672) projection: few output tiles, so K is split and the
+    float partials are summed by the reduce kernel; AUTO dispatch must pick the tcgen05 kernel."""
+    m, k, n = 64, 8192, 28672 // 8
+    rng = np.random.default_rng(64)
+    wp, s = O.make_w4(rng, n, k, 32, np.float16)
+    x = torch.randn(m, k, generator=torch.Generator().manual_seed(2)).half()
+    assert _lib.lib().lcq_matmul_select_algo(4, m, n, k, 32, _lib.F16, _lib.F16, _lib.F16) == _lib.ALGO_GEMM_TC
+    wd, sd = torch.from_numpy(wp).cuda(), torch.from_numpy(s).cuda()
+    y = L.quantized_matmul(x.cuda(), wd, sd, 32)
+    ref = _gemm_ref(x.float().numpy(), wp, s)
+    _check16(y.float().cpu().numpy(), ref)
+    assert torch.equal(L.quantized_matmul(x.cuda(), wd, sd, 32), y)      # fixed summation order
+    _device_status_ok()
+
+
 def test_w4a16_gemm_tc_matches_decode_kernel():
     """Same inputs through the decode kernel (M <= 16 chunks) and the tcgen05 kernel."""
     rng = np.random.default_rng(11)
