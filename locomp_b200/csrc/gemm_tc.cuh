@@ -12,7 +12,7 @@
 //     weights therefore cross shared memory once (0.5 B/weight) and never as 2-byte values.
 //   * One thread issues the MMAs; tcgen05.commit releases X stages and TMEM slots and, after
 //     the last k tile, hands the accumulator to four epilogue warps (tcgen05.ld -> global).
-// TMEM map (512 columns): [0, 256) accumulator, [256, 384) four A slots of 32 columns
+// TMEM map (512 columns): [0, 256) accumulator, [256, 512) eight A slots of 32 columns
 // (64 k as packed fp16 pairs).  Weight tiles are fp16 because bf16's 8-bit significand
 // cannot hold (q-8)*s within the 1e-2 output tolerance; bf16 activations are converted to
 // fp16 by a small pre-pass into the caller's workspace.
@@ -33,7 +33,7 @@ constexpr int S_STAGE = BN * (WK / 32) * 2;   // 2048
 constexpr int WS_STAGE = W_STAGE + S_STAGE;
 constexpr int NXS = 4;                  // X stages
 constexpr int NWS = 2;                  // packed-weight stages
-constexpr int NAS = 4;                  // TMEM A slots
+constexpr int NAS = 8;                  // TMEM A slots
 constexpr int A_COL0 = 256;             // first TMEM column of the A ring
 constexpr int A_SLOT_COLS = 32;
 constexpr int TMEM_COLS = 512;
