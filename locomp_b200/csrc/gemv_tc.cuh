@@ -114,7 +114,7 @@ __host__ __device__ inline int contributors(const Params& p, int rb) {
 }
 
 struct SmemLayout {     // offsets from the 1024-byte aligned base
-  int xs;       // staged activations: [group][M][4] x 16 B, then one 64-byte block of zeros
+  int xs;       // staged activations: [group][M][4] x 16 B (+ 64 spare bytes)
   int corr;     // zero-point operands: [tile][MT][8 m][4 t] x 8 B  (hi pair, lo pair)
   int bars;     // full[NSTAGES], empty[NSTAGES]
   int flags;    // abort flag
@@ -215,7 +215,7 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
       const int oct_per_row = need_tiles * (KT / 8);
       const int total = p.M * oct_per_row;
       const long long kbase = static_cast<long long>(kr) * p.S * KT;
-      // zero the zero-point operands (rows m >= M stay zero) and the block of zeros behind xs
+      // zero the zero-point operands (rows m >= M stay zero)
       {
         uint4* z = reinterpret_cast<uint4*>(smem + L.corr - 64);
         const int zero16 = (L.bars - (L.corr - 64)) / 16;
@@ -302,15 +302,15 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     // chunk c of that row sits at  lane_off ^ (c << 4)   (rows r0 and r0+8 share r & 7)
     const uint32_t lane_off = static_cast<uint32_t>(r0 * 128 + 4 * t4) ^ (static_cast<uint32_t>(g & 7) << 4);
     // x fragment of lane (g, t4) for m tile jm: row m = 8*jm + g of group grp sits at
-    // xs[(grp*M + m)*4 + t4]; lanes whose m does not exist read the block of zeros (stride 0)
+    // xs[(grp*M + m)*4 + t4].  A lane whose m does not exist reads row M-1 instead: B column m only
+    // feeds D column m, and columns >= M are never stored.
     const uint4* xs_lane[MT];
-    int xs_stride[MT];
 #pragma unroll
     for (int jm = 0; jm < MT; ++jm) {
-      const bool has = (8 * jm + g) < p.M;
-      xs_lane[jm] = has ? xs + (8 * jm + g) * 4 + t4 : xs + p.S * GT * p.M * 4;
-      xs_stride[jm] = has ? p.M * 4 : 0;
+      const int m = (8 * jm + g) < p.M ? (8 * jm + g) : p.M - 1;
+      xs_lane[jm] = xs + m * 4 + t4;
     }
+    const int xs_stride = (NC == 1) ? 4 : p.M * 4;     // uint4 per group; NC == 1 means M == 1
     const uint2* corr_lane = reinterpret_cast<const uint2*>(corr) + g * 4 + t4;  // + (tile*MT + jm)*32
 
     bool dead = false;
@@ -344,17 +344,17 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
         }
         const uint4* xp[MT];
 #pragma unroll
-        for (int jm = 0; jm < MT; ++jm) xp[jm] = xs_lane[jm] + ks * GT * xs_stride[jm];
+        for (int jm = 0; jm < MT; ++jm) xp[jm] = xs_lane[jm] + ks * GT * xs_stride;
+        const uint32_t tile_off = static_cast<uint32_t>(s * STAGE_BYTES) + lane_off;   // stage bases are 1024-aligned: the XOR below only flips chunk bits
 #pragma unroll
         for (int c = 0; c < GT; ++c) {
-          const uint32_t off = lane_off ^ (static_cast<uint32_t>(c) << 4);
-          const uint32_t wa = *reinterpret_cast<const uint32_t*>(ws + off);
-          const uint32_t wb = *reinterpret_cast<const uint32_t*>(ws + off + 1024);
+          const uint32_t off = tile_off ^ (static_cast<uint32_t>(c) << 4);
+          const uint32_t wa = *reinterpret_cast<const uint32_t*>(smem + off);
+          const uint32_t wb = *reinterpret_cast<const uint32_t*>(smem + off + 1024);
           const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
 #pragma unroll
           for (int jm = 0; jm < MT; ++jm) {
-            const uint4 bx = *xp[jm];
-            xp[jm] += xs_stride[jm];
+            const uint4 bx = xp[jm][c * xs_stride];
             float d[4];
             mma_m16n8k16_f16(d, wa & 0x000F000Fu, wb & 0x000F000Fu, wa & 0x00F000F0u, wb & 0x00F000F0u,
                              bx.x, bx.y, zero4);
