@@ -330,3 +330,21 @@ def test_decode_stack_counts_and_graph():
     for a, c in zip(eager, st.calls):
         assert torch.equal(a, c[2])
     _device_status_ok()
+
+
+def test_w4a16_gemm_tc_unaligned_n_and_caller_workspace():
+    """N not a multiple of 8 (scalar epilogue stores) and a caller-provided scratch buffer."""
+    m, n, k = 48, 100, 512
+    rng = np.random.default_rng(5)
+    wp, s = O.make_w4(rng, n, k, 32, np.float16)
+    x = torch.randn(m, k, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    wd, sd = torch.from_numpy(wp).cuda(), torch.from_numpy(s).cuda()
+    from locomp_b200.ops import matmul_workspace_bytes
+    need = matmul_workspace_bytes(m, n, k, 32, 4, "bf16", "f16", "bf16", "gemm_tc")
+    assert need > 0
+    ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
+    y = L.quantized_matmul(x.cuda(), wd, sd, 32, algo="gemm_tc", workspace_buf=ws)
+    _check16(y.float().cpu().numpy(), _gemm_ref(x.float().numpy(), wp, s))
+    with pytest.raises(ValueError):
+        L.quantized_matmul(x.cuda(), wd, sd, 32, algo="gemm_tc", workspace_buf=ws[: need // 2])
+    _device_status_ok()
