@@ -266,9 +266,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         import datetime
         import torch.distributed as dist_mod
         dist = dist_mod
-        # Multi-GPU runs: no programmatic dependent launch next to NCCL kernels, and a short collective
-        # timeout so a stuck rank ends the run instead of holding eight GPUs.
-        os.environ["LCQ_NO_PDL"] = "1"
+        # Multi-GPU runs: no programmatic dependent launch next to NCCL kernels (it stays on with the
+        # library's own all-gather kernel), and a short collective timeout so a stuck rank ends the run
+        # instead of holding eight GPUs.
+        if args.gather != "nvlink":
+            os.environ["LCQ_NO_PDL"] = "1"
         os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "1")
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     peaks = load_peaks()
@@ -303,9 +305,19 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         for c in calls:
             c.bind(ws)
     gathered = None
+    peer = None
     if world > 1:
         gathered = [torch.empty(world, c.m, c.n, dtype=c.out.dtype, device=dev) for c in sets[0]]
+        if args.gather == "nvlink":
+            # one peer-memory region per call of a step; a region is pushed to again only one step later
+            peer = [L.PeerGather(c.m * c.n * c.out.element_size()) for c in sets[0]]
     torch.cuda.synchronize()
+
+    def gather_call(ci, c):
+        if peer is not None:
+            peer[ci].push(c.out, stream=torch.cuda.current_stream().cuda_stream)
+        else:
+            dist.all_gather_into_tensor(gathered[ci].view(world * c.m, c.n), c.out)
 
     stream = torch.cuda.Stream(device=dev)
     sp = stream.cuda_stream
@@ -314,7 +326,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         for ci, c in enumerate(sets[si]):
             c.launch(sp)
             if world > 1:
-                dist.all_gather_into_tensor(gathered[ci].view(world * c.m, c.n), c.out)
+                gather_call(ci, c)
 
     # eager warm-up (also sets kernel attributes before any graph capture)
     with torch.cuda.stream(stream):
@@ -322,6 +334,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             step_eager(si)
     torch.cuda.synchronize()
     _lib.check(lib.lcq_check_device_status(None))
+    if peer is not None:
+        # one-time check of the peer-memory all-gather against NCCL on the last warm-up outputs
+        for ci, c in enumerate(sets[nsets - 1]):
+            dist.all_gather_into_tensor(gathered[ci].view(world * c.m, c.n), c.out)
+            got = peer[ci].gathered(c.out.dtype, (world, c.m, c.n))
+            if not torch.equal(got, gathered[ci]):
+                raise RuntimeError(f"peer all-gather mismatch on call {ci}")
+        torch.cuda.synchronize()
 
     graphs = None
     graph_note = "eager"
@@ -335,7 +355,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                     for ci, c in enumerate(sets[si]):
                         c.launch(cap)
                         if world > 1:
-                            dist.all_gather_into_tensor(gathered[ci].view(world * c.m, c.n), c.out)
+                            gather_call(ci, c)
                 graphs.append(g)
             torch.cuda.synchronize()
             graph_note = "cuda_graph"
@@ -398,7 +418,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "shapes_KN": shapes if len(shapes) <= 16 else "30 x " + str(CFG3_LAYER) + " + " + str(CFG3_LM_HEAD), "M": ms, "calls_per_step": len(shapes) * len(ms), "group_size": GROUP,
             "l2_hygiene": f"every call reads its own weights; {nsets} rotating sets of {per_set_bytes / 1e6:.0f} MB",
             "launch": graph_note,
-            "sharding": None if world == 1 else f"N-column shards + NCCL all-gather, {world} ranks",
+            "sharding": None if world == 1 else (f"N-column shards + " + ("NVLink peer-store all-gather kernel" if peer is not None else "NCCL all-gather") + f", {world} ranks"),
         },
         "gpu_launches": args.steps * len(shapes) * len(ms),
         "weight_bytes_per_step": per_set_bytes * world,
@@ -555,6 +575,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--gather", default="nccl", choices=["nccl", "nvlink"],
+                    help="multi-GPU: reassemble outputs with NCCL or with the library's peer-store kernel")
     ap.add_argument("--watchdog", type=int, default=900, help="abort the process after this many seconds")
     ap.add_argument("--profile-shape", default=None, metavar="KxNxM",
                     help="run a few launches of one problem and exit (small case for ncu captures)")

@@ -142,6 +142,29 @@ int lcq_matmul_int4_noalloc(const void* x, const void* w_packed, const void* sca
 size_t lcq_noalloc_scratch_bytes(void);
 
 /*
+ * All-gather over NVLink peer memory for N-column sharded linears (one process per GPU).  No
+ * counterpart in the reference, which has no multi-GPU code.
+ *
+ * Each rank owns one region of lcq_peer_region_bytes(bytes_per_rank, world) bytes:
+ * [256 bytes of flags][world slices].  lcq_peer_alloc allocates it (cudaMalloc, zero-filled -- a
+ * set-up call, not for the hot path) and returns a 64-byte CUDA IPC handle to hand to the other
+ * ranks; lcq_peer_open maps a peer's region from its handle.  lcq_allgather_push(src, ...,
+ * regions[0..world-1], rank, world, state, stream) enqueues ONE kernel that stores this rank's
+ * slice into slot `rank` of every region (peer stores only, never peer loads), publishes a
+ * sequence number and waits -- bounded; on expiry lcq_check_device_status reports it -- until this
+ * rank's own region holds every rank's slice of the same call.  `state`: 2 zero-initialised ints of
+ * local device memory per region.  All ranks must issue the same sequence of pushes per region.
+ * world <= 8; slices are multiples of 16 bytes.
+ */
+int lcq_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64);
+int lcq_peer_open(const unsigned char* handle64, void** ptr);
+int lcq_peer_close(void* ptr);
+int lcq_peer_free(void* ptr);
+int lcq_allgather_push(const void* src, size_t bytes_per_rank, void* const* regions, int rank, int world,
+                       void* state, void* stream);
+size_t lcq_peer_region_bytes(size_t bytes_per_rank, int world);
+
+/*
  * Device-side status word.  Kernels that wait on an mbarrier do so with an iteration limit;
  * when a wait gives up the kernel records it here and returns instead of hanging.  Reads the
  * word of the current device (synchronising `stream` first), clears it and returns LCQ_OK or

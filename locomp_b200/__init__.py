@@ -9,13 +9,13 @@ from ._lib import LcqError
 from .ops import (dequant_int4, dequant_int8, dequant_matvec_int4, dequant_matvec_int8, dequantize,
                   gpu_dequant_int4, gpu_dequant_int8, gpu_matvec_int4, gpu_matvec_int8, quantized_matmul)
 from .linear import DecodeStack, QuantLinear, fuse_rows
-from .shard import ShardedQuantLinear, shard_rows
+from .shard import PeerGather, ShardedQuantLinear, shard_rows
 from .tensor import DeviceTensor, empty, tensor, zeros
 
 __all__ = [
     "LcqError", "DeviceTensor", "tensor", "empty", "zeros",
     "gpu_matvec_int4", "gpu_matvec_int8", "gpu_dequant_int4", "gpu_dequant_int8",
     "dequant_matvec_int4", "dequant_matvec_int8", "dequant_int4", "dequant_int8",
-    "quantized_matmul", "dequantize", "ShardedQuantLinear", "shard_rows", "QuantLinear", "fuse_rows", "DecodeStack",
+    "quantized_matmul", "dequantize", "ShardedQuantLinear", "PeerGather", "shard_rows", "QuantLinear", "fuse_rows", "DecodeStack",
 ]
 __version__ = "0.1.0"

@@ -32,6 +32,13 @@ SIGNATURES = {
     "lcq_matmul_select_algo": (_c.c_int, [_c.c_int] * 8),
     "lcq_matmul_int4_noalloc": (_c.c_int, [_c.c_void_p] * 4 + [_c.c_int] * 7 + [_c.c_void_p]),
     "lcq_noalloc_scratch_bytes": (_c.c_size_t, []),
+    "lcq_peer_alloc": (_c.c_int, [_c.c_size_t, _c.POINTER(_c.c_void_p), _c.c_char_p]),
+    "lcq_peer_open": (_c.c_int, [_c.c_char_p, _c.POINTER(_c.c_void_p)]),
+    "lcq_peer_close": (_c.c_int, [_c.c_void_p]),
+    "lcq_peer_free": (_c.c_int, [_c.c_void_p]),
+    "lcq_allgather_push": (_c.c_int, [_c.c_void_p, _c.c_size_t, _c.POINTER(_c.c_void_p), _c.c_int, _c.c_int,
+                                      _c.c_void_p, _c.c_void_p]),
+    "lcq_peer_region_bytes": (_c.c_size_t, [_c.c_size_t, _c.c_int]),
     "lcq_check_device_status": (_c.c_int, [_c.c_void_p]),
     "lcq_gemv_tc_plan_check": (_c.c_int, [_c.c_int] * 4 + [_c.POINTER(_c.c_int)]),
 }

@@ -10,6 +10,7 @@
 #include "gemv_simt.cuh"
 #include "gemv_tc.cuh"
 #include "gemm_tc.cuh"
+#include "peer_gather.cuh"
 
 namespace lcq {
 
@@ -437,6 +438,69 @@ int lcq_matmul_int4_noalloc(const void* x, const void* w_packed, const void* sca
 }
 
 size_t lcq_noalloc_scratch_bytes(void) { return LCQ_NOALLOC_SCRATCH_BYTES; }
+
+// ---------------------------------------------------------------- NVLink peer all-gather
+int lcq_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64) {
+  if (!ptr || !handle64 || bytes == 0) { set_error("lcq_peer_alloc: bad argument"); return LCQ_ERR_BAD_ARG; }
+  void* p = nullptr;
+  LCQ_CUDA_TRY(cudaMalloc(&p, bytes));
+  cudaError_t e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) { cudaFree(p); return cuda_fail(e, "lcq_peer_alloc"); }
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  memcpy(handle64, &h, 64);
+  *ptr = p;
+  return LCQ_OK;
+}
+
+int lcq_peer_open(const unsigned char* handle64, void** ptr) {
+  if (!ptr || !handle64) { set_error("lcq_peer_open: bad argument"); return LCQ_ERR_BAD_ARG; }
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  LCQ_CUDA_TRY(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return LCQ_OK;
+}
+
+int lcq_peer_close(void* ptr) {
+  LCQ_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+  return LCQ_OK;
+}
+
+int lcq_peer_free(void* ptr) {
+  LCQ_CUDA_TRY(cudaFree(ptr));
+  return LCQ_OK;
+}
+
+int lcq_allgather_push(const void* src, size_t bytes_per_rank, void* const* regions, int rank, int world,
+                       void* state, void* stream) {
+  if (!src || !regions || !state || world < 1 || world > peer::MAX_RANKS || rank < 0 || rank >= world) {
+    set_error("lcq_allgather_push: bad argument (world must be 1..%d)", peer::MAX_RANKS);
+    return LCQ_ERR_BAD_ARG;
+  }
+  if (bytes_per_rank == 0 || bytes_per_rank % 16 != 0 || !aligned(src, 16)) {
+    set_error("lcq_allgather_push: slices must be 16-byte aligned multiples of 16 bytes");
+    return LCQ_ERR_BAD_ARG;
+  }
+  peer::PushArgs a;
+  memset(&a, 0, sizeof(a));
+  for (int g = 0; g < world; ++g) {
+    if (!regions[g]) { set_error("lcq_allgather_push: region %d is null", g); return LCQ_ERR_BAD_ARG; }
+    a.flags[g] = static_cast<int*>(regions[g]);
+    a.data[g] = reinterpret_cast<uint4*>(static_cast<uint8_t*>(regions[g]) + peer::FLAG_BYTES);
+  }
+  a.src = static_cast<const uint4*>(src);
+  a.n16 = static_cast<long long>(bytes_per_rank / 16);
+  a.rank = rank;
+  a.world = world;
+  a.state = static_cast<int*>(state);
+  return peer::launch_push(a, static_cast<cudaStream_t>(stream));
+}
+
+size_t lcq_peer_region_bytes(size_t bytes_per_rank, int world) {
+  return peer::FLAG_BYTES + bytes_per_rank * static_cast<size_t>(world);
+}
 
 int lcq_check_device_status(void* stream) {
   LCQ_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));

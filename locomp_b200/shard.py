@@ -19,6 +19,85 @@ import torch
 import torch.distributed as dist
 
 
+class PeerGather:
+    """All-gather of equal slices over NVLink peer memory (see include/locomp_b200.h,
+    lcq_allgather_push): every rank pushes its slice into every rank's region with one kernel.
+
+    One instance owns one region on this rank plus mappings of the peers' regions.  Set-up
+    (allocation, exchange of CUDA IPC handles through the process group, a barrier) happens in the
+    constructor; `push(src)` is the hot call: one kernel launch, no allocation, no NCCL.
+    """
+
+    def __init__(self, bytes_per_rank: int, group: Optional[dist.ProcessGroup] = None):
+        import ctypes
+        from . import _lib
+        self._lib, self._ct = _lib, ctypes
+        L = _lib.lib()
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if bytes_per_rank <= 0 or bytes_per_rank % 16:
+            raise ValueError("slices must be a positive multiple of 16 bytes")
+        if self.world > 8:
+            raise ValueError("PeerGather supports up to 8 ranks of one box")
+        self.bytes_per_rank = bytes_per_rank
+        self.device = torch.cuda.current_device()
+        region_bytes = L.lcq_peer_region_bytes(bytes_per_rank, self.world)
+        mine = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        _lib.check(L.lcq_peer_alloc(region_bytes, ctypes.byref(mine), handle))
+        self._mine = mine.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self._regions = (ctypes.c_void_p * self.world)()
+        self._opened = []
+        for r in range(self.world):
+            if r == self.rank:
+                self._regions[r] = self._mine
+            else:
+                p = ctypes.c_void_p()
+                _lib.check(L.lcq_peer_open(handles[r], ctypes.byref(p)))
+                self._regions[r] = p.value
+                self._opened.append(p.value)
+        self._state = torch.zeros(2, dtype=torch.int32, device=torch.device("cuda", self.device))
+        torch.cuda.synchronize()
+        dist.barrier(group=group)                   # every region is mapped everywhere before the first push
+
+    def gathered(self, dtype: torch.dtype, shape) -> torch.Tensor:
+        """Zero-copy torch view of this rank's gathered data area ([world, ...slice shape])."""
+        class _Mem:
+            pass
+        m = _Mem()
+        n = 1
+        for d in shape:
+            n *= d
+        itemsize = torch.empty(0, dtype=dtype).element_size()
+        if n * itemsize != self.world * self.bytes_per_rank:
+            raise ValueError("shape does not match the region")
+        m.__cuda_array_interface__ = {"shape": (self.world * self.bytes_per_rank,), "typestr": "|u1",
+                                      "data": (self._mine + 256, False), "version": 3}
+        self._keep = m
+        return torch.as_tensor(m, device=torch.device("cuda", self.device)).view(dtype).view(*shape)
+
+    def push(self, src: torch.Tensor, stream=None) -> None:
+        """Enqueue the all-gather of `src` (this rank's slice, contiguous, bytes_per_rank bytes)."""
+        if src.numel() * src.element_size() != self.bytes_per_rank or not src.is_contiguous():
+            raise ValueError("src must be a contiguous tensor of bytes_per_rank bytes")
+        sp = torch.cuda.current_stream().cuda_stream if stream is None else int(stream)
+        self._lib.check(self._lib.lib().lcq_allgather_push(src.data_ptr(), self.bytes_per_rank, self._regions,
+                                                           self.rank, self.world, self._state.data_ptr(), sp))
+
+    def close(self) -> None:
+        L = self._lib.lib()
+        torch.cuda.synchronize()
+        for p in self._opened:
+            L.lcq_peer_close(p)
+        self._opened = []
+        if self._mine:
+            L.lcq_peer_free(self._mine)
+            self._mine = None
+
+
 def shard_rows(n: int, world: int, rank: int) -> Tuple[int, int]:
     """Row range [r0, r1) of W owned by `rank`.  N must divide evenly so every rank gathers equal blocks."""
     if world < 1 or not (0 <= rank < world):
@@ -39,7 +118,8 @@ class ShardedQuantLinear:
     """
 
     def __init__(self, w, scales, group_size: int = 32, bits: int = 4, group: Optional[dist.ProcessGroup] = None,
-                 already_local: bool = False, n_total: Optional[int] = None, matmul: Optional[Callable] = None):
+                 already_local: bool = False, n_total: Optional[int] = None, matmul: Optional[Callable] = None,
+                 gather: str = "nccl"):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -60,6 +140,10 @@ class ShardedQuantLinear:
             matmul = quantized_matmul
         self._matmul = matmul
         self._gather_buf = None
+        if gather not in ("nccl", "nvlink"):
+            raise ValueError("gather must be 'nccl' or 'nvlink'")
+        self.gather = gather            # "nvlink": PeerGather (peer stores), two regions used alternately
+        self._peer = {}                 # (m, dtype) -> [PeerGather, PeerGather], next index
 
     def local(self, x, **kw):
         """This rank's columns only: [M, N/G]."""
@@ -74,6 +158,16 @@ class ShardedQuantLinear:
         m = y.shape[0]
         if self.world == 1:
             full = y.unsqueeze(0)
+        elif self.gather == "nvlink":
+            key = (m, y.dtype)
+            if key not in self._peer:
+                nbytes = m * self.n_local * y.element_size()
+                self._peer[key] = [[PeerGather(nbytes, self.group), PeerGather(nbytes, self.group)], 0]
+            pair, nxt = self._peer[key]
+            pg = pair[nxt]
+            self._peer[key][1] = nxt ^ 1          # back-to-back calls alternate regions
+            pg.push(y.contiguous())
+            full = pg.gathered(y.dtype, (self.world, m, self.n_local))
         else:
             buf = self._gather_buf
             if buf is None or buf.shape != (self.world, m, self.n_local) or buf.dtype != y.dtype or buf.device != y.device:
