@@ -122,3 +122,32 @@ def test_no_cpu_fallback():
         pytest.skip("a GPU is present")
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         L.gpu_matvec_int4(np.zeros(64, np.float32), np.zeros((4, 32), np.uint8), np.zeros((4, 2), np.float32))
+
+
+def test_foreign_cuda_tensor_objects_are_validated():
+    """Objects shaped like the reference's CUDATensor (_cuda_ptr / dtype / shape) are accepted by the
+    argument normaliser and checked like any other operand -- before any launch."""
+    from locomp_b200.tensor import resolve
+
+    class FakeCUDATensor:
+        def __init__(self, ptr, shape, dtype):
+            self._cuda_ptr, self.shape, self.dtype, self.size = ptr, shape, np.dtype(dtype), int(np.prod(shape))
+
+    op = resolve(FakeCUDATensor(0x1000, (4, 32), np.uint8), "w")
+    assert op.ptr == 0x1000 and op.kind == "u8" and op.shape == (4, 32) and op.size == 128
+    assert resolve(FakeCUDATensor(0x2000, (64,), np.float16), "x", bf16=True).kind == "bf16"
+    with pytest.raises(TypeError):
+        resolve(FakeCUDATensor(0x1000, (4,), np.float64), "x")
+    with pytest.raises(TypeError):
+        resolve(object(), "x")
+    # shape errors surface before the device is touched, also for foreign tensors
+    with pytest.raises(ValueError, match="K=64"):
+        L.gpu_matvec_int4(FakeCUDATensor(0x1000, (64,), np.float32), FakeCUDATensor(0x2000, (4, 31), np.uint8),
+                          FakeCUDATensor(0x3000, (4, 2), np.float32))
+
+
+def test_sharding_argument_checks():
+    from locomp_b200.shard import shard_rows
+    assert shard_rows(49152, 8, 7) == (43008, 49152)
+    with pytest.raises(ValueError):
+        L.ShardedQuantLinear(np.zeros((4, 32), np.uint8), np.zeros((4, 2), np.float16), gather="smoke-signals")
