@@ -173,6 +173,14 @@ size_t lcq_peer_region_bytes(size_t bytes_per_rank, int world);
 int lcq_check_device_status(void* stream);
 
 /*
+ * Sets, for the CURRENT device, how long a kernel of this library waits (on an mbarrier or on a
+ * peer's flag) before it gives up, records the failure for lcq_check_device_status and returns.
+ * Default 2,000,000,000 ns.  Synchronises the device (it writes a device variable); a set-up call.
+ * No counterpart in the reference.
+ */
+int lcq_set_wait_limit_ns(unsigned long long limit_ns);
+
+/*
  * Diagnostic, host only: builds the work plan the GEMV_TC kernel would use for (M, N, K) on a
  * device with sm_count SMs and replays its device-side schedule on the CPU, checking that
  * every (row block, k tile) is produced exactly once and that scratch slots and contributor

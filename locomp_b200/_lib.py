@@ -40,6 +40,7 @@ SIGNATURES = {
                                       _c.c_void_p, _c.c_void_p]),
     "lcq_peer_region_bytes": (_c.c_size_t, [_c.c_size_t, _c.c_int]),
     "lcq_check_device_status": (_c.c_int, [_c.c_void_p]),
+    "lcq_set_wait_limit_ns": (_c.c_int, [_c.c_ulonglong]),
     "lcq_gemv_tc_plan_check": (_c.c_int, [_c.c_int] * 4 + [_c.POINTER(_c.c_int)]),
 }
 

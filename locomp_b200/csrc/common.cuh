@@ -15,7 +15,7 @@
 namespace lcq {
 
 // ------------------------------------------------------------------ host-side error plumbing
-void set_error(const char* fmt, ...);          // stores a thread-local message (capi.cu)
+void set_error(const char* fmt, ...);          // stores a thread-local message (defined in lib.cu)
 int cuda_fail(cudaError_t e, const char* what); // stores the message, returns LCQ_ERR_CUDA
 
 #define LCQ_CUDA_TRY(expr)                                            \
@@ -80,23 +80,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: returns false (and the caller must unwind) if the phase does not complete
-// within about two seconds of wall-clock time.  try_wait itself suspends the thread for a
-// hardware-defined interval, so the loop is not a hot spin.
+// within the wait limit (two seconds of wall-clock time unless lcq_set_wait_limit_ns changed
+// it).  try_wait itself suspends the thread for a hardware-defined interval, so the loop is
+// not a hot spin; the limit is read from device memory only on the slow path.
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+__device__ unsigned long long g_wait_limit_ns = 2000000000ull;
+__device__ __forceinline__ uint64_t wait_limit_ns() { return *reinterpret_cast<volatile unsigned long long*>(&g_wait_limit_ns); }
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
+  const uint64_t limit = wait_limit_ns();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
     }
-    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+    if (global_timer_ns() - t0 > limit) return false;
   }
 }
 __device__ __forceinline__ void fence_barrier_init() {

@@ -512,8 +512,8 @@ inline int launch(const void* x, const void* w, const void* s, void* out, int M,
   }
   uint8_t* scratch = need ? static_cast<uint8_t*>(workspace) + kWorkspaceCounterBytes : nullptr;
   const void* xh = x;
-  // (A mixed fp16 x bf16 MMA was tried in place of this copy: it gave wrong results and a CUDA
-  //  error on B200, so bf16 activations always take the fp16 copy.)
+  // kind::f16 wants both operands in one 16-bit format and the weight tiles must be fp16, so bf16
+  // activations are converted once into the workspace.
   if (x_dtype == LCQ_BF16) {
     const long long n16 = static_cast<long long>(M) * K / 8;
     long long blocks = (n16 + 255) / 256;

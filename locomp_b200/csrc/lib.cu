@@ -177,6 +177,17 @@ static int simt_entry(const void* x, const void* w, const void* s, void* out, in
   return LCQ_ERR_BAD_ARG;
 }
 
+// Scratch the decode kernel needs for M rows: the call runs in chunks of 16 rows plus one tail
+// chunk of M % 16 rows, and the tail's plan can need more scratch than a full chunk's.
+static size_t gemv_tc_workspace_bytes(int M, int N, int K, int sm_count) {
+  size_t need = gemv_tc::make_plan(M < 16 ? M : 16, N, K, sm_count).workspace_bytes;
+  if (M > 16 && (M % 16) != 0) {
+    const size_t tail = gemv_tc::make_plan(M % 16, N, K, sm_count).workspace_bytes;
+    if (tail > need) need = tail;
+  }
+  return need;
+}
+
 static int select_algo(int wbits, int M, int N, int K, int G, int x_dtype, int scale_dtype, int out_dtype) {
   (void)out_dtype;
   if (wbits == 4 && M > 16 && gemm_tc::supported(M, N, K, G, x_dtype, scale_dtype)) return LCQ_ALGO_GEMM_TC;
@@ -213,8 +224,17 @@ static int matmul_entry(int wbits, const void* x, const void* w, const void* s, 
         set_error("GEMV_TC needs int4, group_size 32, K %% 256 == 0, f16 scales, f16/bf16 x");
         return LCQ_ERR_UNSUPPORTED;
       }
-      // M > 16: rows of x in chunks of 16 (each chunk re-streams the weights)
+      // M > 16: rows of x in chunks of 16 (each chunk re-streams the weights).  Every chunk's plan
+      // is checked against the workspace before the first launch, so a call either runs whole
+      // or not at all.
       const size_t xe = 2, oe = out_dtype == LCQ_F32 ? 4 : 2;
+      {
+        const size_t need = gemv_tc_workspace_bytes(M, N, K, di.sm_count);
+        if (workspace == nullptr || workspace_bytes < need) {
+          set_error("w4a16 gemv: workspace of %zu bytes (256-byte aligned) required, got %zu", need, workspace_bytes);
+          return LCQ_ERR_WORKSPACE;
+        }
+      }
       for (int m0 = 0; m0 < M; m0 += 16) {
         const int mc = M - m0 < 16 ? M - m0 : 16;
         rc = gemv_tc::launch(static_cast<const uint8_t*>(x) + static_cast<size_t>(m0) * K * xe, w, s,
@@ -319,7 +339,7 @@ size_t lcq_matmul_workspace_bytes(int wbits, int M, int N, int K, int group_size
   if (algo == LCQ_ALGO_GEMV_TC) {
     if (wbits != 4 || !gemv_tc::supported(M < 16 ? M : 16, N, K, group_size, x_dtype, scale_dtype))
       return static_cast<size_t>(-1);
-    return gemv_tc::make_plan(M < 16 ? M : 16, N, K, sm).workspace_bytes;
+    return gemv_tc_workspace_bytes(M, N, K, sm);
   }
   if (algo == LCQ_ALGO_GEMM_TC) {
     if (wbits != 4 || !gemm_tc::supported(M, N, K, group_size, x_dtype, scale_dtype)) return static_cast<size_t>(-1);
@@ -500,6 +520,12 @@ int lcq_allgather_push(const void* src, size_t bytes_per_rank, void* const* regi
 
 size_t lcq_peer_region_bytes(size_t bytes_per_rank, int world) {
   return peer::FLAG_BYTES + bytes_per_rank * static_cast<size_t>(world);
+}
+
+int lcq_set_wait_limit_ns(unsigned long long limit_ns) {
+  if (limit_ns == 0) { set_error("lcq_set_wait_limit_ns: the limit must be positive"); return LCQ_ERR_BAD_ARG; }
+  LCQ_CUDA_TRY(cudaMemcpyToSymbol(g_wait_limit_ns, &limit_ns, sizeof(limit_ns)));
+  return LCQ_OK;
 }
 
 int lcq_check_device_status(void* stream) {

@@ -7,16 +7,20 @@
 //   1. copies this rank's slice into slot `rank` of every region (its own included),
 //   2. after the last CTA's stores are fenced system-wide, writes the call's sequence number
 //      into flags[rank] of every region,
-//   3. waits -- bounded, ~2 s -- until its own region shows that sequence number from every
+//   3. waits -- bounded by the library's wait limit -- until its own region shows that sequence number from every
 //      rank, so kernels that follow on the stream see the complete gathered buffer.
 // The sequence number lives in device memory and is advanced by the kernel itself, so a CUDA
 // graph that captured the launch can be replayed.  Ranks run on different GPUs (one process per
 // GPU); the wait is on other GPUs' kernels, never on another launch of the same GPU.
 //
-// Reuse rule: a region may be pushed to again only after the consumers of its previous contents
-// have been ENQUEUED ahead of the next push on every rank's stream and at least one other
-// push/wait round on a different region has passed in between (the bench's twelve linears per
-// step do that); a layer called back to back alternates between two regions.
+// Reuse rule: a rank's push overwrites slot `rank` of EVERY rank's region as soon as it runs, so
+// a region may be pushed to again only when no rank can still be reading its previous contents.
+// A rank leaves push k only after it has seen every rank's flag of push k, i.e. every rank has
+// at least started push k; it has not necessarily finished reading the data of push k-1 on the
+// same region.  So between two pushes to one region there must be (a) the readers of the first,
+// enqueued ahead of the second push on every rank's stream, and (b) one complete push/wait round
+// on a DIFFERENT region, which proves that every rank's stream has passed those readers.  A
+// layer called back to back therefore alternates between two regions.
 #pragma once
 #include "common.cuh"
 
@@ -72,10 +76,11 @@ __global__ void __launch_bounds__(256) allgather_push_kernel(const PushArgs a) {
   a.state[0] = seq;
   for (int g = 0; g < a.world; ++g) st_release_sys(a.flags[g] + a.rank, seq);
   const uint64_t t0 = global_timer_ns();
+  const uint64_t limit = wait_limit_ns();
   const int* mine = a.flags[a.rank];
   for (int r = 0; r < a.world; ++r) {
     while (ld_acquire_sys(mine + r) - seq < 0) {                     // wrap-safe "not yet"
-      if (global_timer_ns() - t0 > kWaitLimitNs) { atomicExch(&g_device_status, 30 + r); return; }
+      if (global_timer_ns() - t0 > limit) { atomicExch(&g_device_status, 30 + r); return; }
     }
   }
 }

@@ -145,12 +145,48 @@ class ShardedQuantLinear:
         self.gather = gather            # "nvlink": PeerGather (peer stores), two regions used alternately
         self._peer = {}                 # (m, dtype) -> [PeerGather, PeerGather], next index
 
+    def prepare(self, m: int, dtype: torch.dtype) -> None:
+        """Set up what `forward` needs for M = m outputs of `dtype`, so that the hot call allocates
+        nothing and runs no collective of its own: with gather="nvlink" the two peer-memory regions
+        (a cudaMalloc, an exchange of IPC handles through the process group and a barrier -- every
+        rank must call prepare with the same arguments); with gather="nccl" the gathered buffer.
+        Call it before capturing `forward` in a CUDA graph."""
+        if self.world == 1:
+            return
+        if self.gather == "nvlink":
+            key = (m, dtype)
+            if key not in self._peer:
+                nbytes = m * self.n_local * torch.empty(0, dtype=dtype).element_size()
+                self._peer[key] = [[PeerGather(nbytes, self.group), PeerGather(nbytes, self.group)], 0]
+        else:
+            dev = self.w.device
+            buf = self._gather_buf
+            if buf is None or buf.shape != (self.world, m, self.n_local) or buf.dtype != dtype:
+                self._gather_buf = torch.empty((self.world, m, self.n_local), dtype=dtype, device=dev)
+
+    def close(self) -> None:
+        """Release the peer-memory regions (every rank, after its last forward has completed).
+        Destroy CUDA graphs that captured `forward` first, and call this -- and destroy those
+        graphs -- before torch.distributed.destroy_process_group(): a graph that still holds
+        captured NCCL work keeps the communicator busy and its destruction then blocks."""
+        for pair, _ in self._peer.values():
+            for pg in pair:
+                pg.close()
+        self._peer = {}
+        self._gather_buf = None
+
     def local(self, x, **kw):
         """This rank's columns only: [M, N/G]."""
         return self._matmul(x, self.w, self.scales, self.group_size, bits=self.bits, **kw)
 
     def forward(self, x, layout: str = "row_major", **kw):
-        """Full output on every rank.  x: [K] or [M, K], replicated on all ranks."""
+        """Full output on every rank.  x: [K] or [M, K], replicated on all ranks.
+
+        Lifetime of the result: with layout="gathered" (and for M = 1, where the row-major form is
+        a view of it) the returned tensor aliases the layer's gather buffer -- with gather="nccl"
+        it is overwritten by the next forward, with gather="nvlink" by the forward after the next
+        (two regions alternate; peers write into them).  Copy it if it must live longer.  For
+        M > 1 layout="row_major" returns a fresh tensor."""
         if layout not in ("row_major", "gathered"):
             raise ValueError("layout must be 'row_major' or 'gathered'")
         squeeze = x.dim() == 1
@@ -161,8 +197,7 @@ class ShardedQuantLinear:
         elif self.gather == "nvlink":
             key = (m, y.dtype)
             if key not in self._peer:
-                nbytes = m * self.n_local * y.element_size()
-                self._peer[key] = [[PeerGather(nbytes, self.group), PeerGather(nbytes, self.group)], 0]
+                self.prepare(m, y.dtype)          # first use: allocates and synchronises the ranks
             pair, nxt = self._peer[key]
             pg = pair[nxt]
             self._peer[key][1] = nxt ^ 1          # back-to-back calls alternate regions

@@ -1,0 +1,47 @@
+"""Failure detection without faulting anything: a device-side wait is made to run out (it waits
+for a flag that nothing sets), the kernel returns on its own, the host reads the error status,
+and the context stays usable."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import locomp_b200 as L
+from locomp_b200 import _lib
+from oracle import qmm_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def test_bounded_wait_runs_out_and_the_context_survives():
+    lib = _lib.lib()
+    assert lib.lcq_set_wait_limit_ns(5_000_000) == 0          # 5 ms instead of 2 s
+    try:
+        nbytes = 4096
+        region_bytes = lib.lcq_peer_region_bytes(nbytes, 2)
+        mine = torch.zeros(region_bytes, dtype=torch.uint8, device="cuda")
+        absent_peer = torch.zeros(region_bytes, dtype=torch.uint8, device="cuda")   # a "rank 1" that never pushes
+        regions = (ctypes.c_void_p * 2)(mine.data_ptr(), absent_peer.data_ptr())
+        state = torch.zeros(2, dtype=torch.int32, device="cuda")
+        src = torch.arange(nbytes, dtype=torch.int32, device="cuda").to(torch.uint8)
+        assert lib.lcq_allgather_push(src.data_ptr(), nbytes, regions, 0, 2, state.data_ptr(), None) == 0
+        assert lib.lcq_check_device_status(None) == _lib.ERR_TIMEOUT
+        assert b"bounded wait" in lib.lcq_last_error()
+        # this rank's slice did arrive in slot 0 of both regions before the wait gave up
+        assert torch.equal(mine[256:256 + nbytes], src) and torch.equal(absent_peer[256:256 + nbytes], src)
+        # the status word was cleared by the read, and the next kernel runs normally
+        assert lib.lcq_check_device_status(None) == 0
+        rng = np.random.default_rng(1)
+        wp, s = O.make_w4(rng, 256, 512, 32, np.float16)
+        x = rng.standard_normal((2, 512)).astype(np.float16)
+        y = L.quantized_matmul(torch.from_numpy(x).cuda(), torch.from_numpy(wp).cuda(), torch.from_numpy(s).cuda(), 32)
+        ref = O.matmul_int4(x.astype(np.float32), wp, s, 32)
+        assert np.all(np.abs(y.float().cpu().numpy() - ref) <= 1e-2 + 1e-2 * np.abs(ref))
+        assert lib.lcq_check_device_status(None) == 0
+    finally:
+        assert lib.lcq_set_wait_limit_ns(2_000_000_000) == 0
+
+
+def test_wait_limit_must_be_positive():
+    assert _lib.lib().lcq_set_wait_limit_ns(0) == _lib.ERR_BAD_ARG

@@ -39,7 +39,7 @@ def _worker(rank, world, port, n, k, m, q):
         layer = ShardedQuantLinear(torch.from_numpy(wp), torch.from_numpy(s), 32, 4, matmul=_oracle_matmul)
         r0, r1 = shard_rows(n, world, rank)
         assert layer.n_local == n // world and tuple(layer.w.shape) == (n // world, k // 2)
-        assert layer.w.data_ptr() == torch.from_numpy(wp)[r0:r1].data_ptr() or True   # view of a row block
+        assert layer.w.untyped_storage().nbytes() == wp.nbytes and layer.w.storage_offset() == r0 * (k // 2)   # a view of the full tensor's row block, not a copy
         full = layer.forward(x)
         ref = O.matmul_int4(x.numpy(), wp, s, 32).astype(np.float32)
         ok = bool(np.allclose(full.numpy(), ref, rtol=1e-6, atol=1e-6)) and tuple(full.shape) == (m, n)
