@@ -142,6 +142,59 @@ int lcq_matmul_int4_noalloc(const void* x, const void* w_packed, const void* sca
 size_t lcq_noalloc_scratch_bytes(void);
 
 /*
+ * Decode-step kernels on either side of the quantized linears.  `dtype` (LCQ_F32 / F16 / BF16) is
+ * the storage type of every tensor of the call; arithmetic is float32, results are rounded once.
+ * All are stream-ordered single kernels that take part in programmatic dependent launch.
+ *
+ * lcq_rms_norm: out[r, i] = x[r, i] * rsqrt(mean_i(x[r, :]^2) + eps) * weight[i], x and out [rows, n].
+ *   Replaces `rms_norm_kernel` (examples/54_smollm2_inference.py:40-73, launched [(rows,),(128,)] with
+ *   N and EPS_X1000 baked in; eps = EPS_X1000 * 1e-6).
+ * lcq_residual_rms_norm: hidden[r, :] += delta[r, :] (in place), then out = rms_norm(hidden) as above:
+ *   `add_inplace_kernel` followed by `rms_norm_kernel` (examples/54_smollm2_inference.py:529-534) in one
+ *   launch; the reference's own fused form is examples/34_fused_residual_norm.py:18-60.
+ * lcq_silu_mul: out[i] = gate[i] * sigmoid(gate[i]) * up[i].  Replaces `silu_mul_kernel`
+ *   (examples/54_smollm2_inference.py:113-120).
+ * lcq_add_inplace: a[i] += b[i].  Replaces `add_inplace_kernel` (examples/54_smollm2_inference.py:164-167).
+ */
+int lcq_rms_norm(const void* x, const void* weight, void* out, int64_t rows, int n, float eps, int dtype, void* stream);
+int lcq_residual_rms_norm(void* hidden, const void* delta, const void* weight, void* out, int64_t rows, int n,
+                          float eps, int dtype, void* stream);
+int lcq_silu_mul(const void* gate, const void* up, void* out, int64_t n, int dtype, void* stream);
+int lcq_add_inplace(void* a, const void* b, int64_t n, int dtype, void* stream);
+
+/*
+ * Embedding lookup: out[t, :] = table[token_ids[t], :]; token_ids int32 [tokens], table [vocab, dim],
+ * out [tokens, dim], both of `dtype`.  Replaces `_embed_fp32` / `_embed_fp16`
+ * (locomp/_builtin_kernels.py:8-25) behind locomp.embed_lookup (locomp/api.py:1025-1038).  An id
+ * outside [0, vocab) gives a row of zeros and is reported by lcq_check_device_status (the reference
+ * reads out of bounds).
+ */
+int lcq_embed_lookup(const void* token_ids, const void* table, void* out, int64_t tokens, int vocab, int dim,
+                     int dtype, void* stream);
+
+/*
+ * Greedy sampling on the device: out[r] (int32) = index of the first maximum of x[r, 0..n), so a
+ * decode loop copies back 4 bytes per token instead of the logits.  Same result as the host-side
+ * np.argmax the reference applies to the downloaded logits (examples/54_smollm2_inference.py:606):
+ * ties go to the lowest index, a NaN counts as the maximum.
+ */
+int lcq_argmax(const void* x, void* out, int64_t rows, int n, int dtype, void* stream);
+
+/*
+ * Weight quantisers with the reference's arithmetic, bit for bit: w [N, K] of `w_dtype` ->
+ * w_packed uint8 [N, K/2] (or w_int8 int8 [N, K]) and scales float32 [N, K/group_size].
+ * style 0 = quantize_int4 / quantize_int8 of examples/38_quantized_matmul.py:248-293
+ *           (scale = amax/7 resp. amax/127, 1.0 for an all-zero group; q = clip(rint(w/scale) [+8]));
+ * style 1 = quantize_int4_ref of examples/52_dequantize.py:110-126 and the int8 form of its self-check
+ *           (:162-165): amax floored at 1e-10 (int4 only), q = clip(rint(w/(scale + 1e-10)) [+8]).
+ * Both are O(N*K) Python loops / NumPy passes in the reference.
+ */
+int lcq_quantize_int4(const void* w, void* w_packed, void* scales, int64_t N, int64_t K, int group_size,
+                      int w_dtype, int style, void* stream);
+int lcq_quantize_int8(const void* w, void* w_int8, void* scales, int64_t N, int64_t K, int group_size,
+                      int w_dtype, int style, void* stream);
+
+/*
  * All-gather over NVLink peer memory for N-column sharded linears (one process per GPU).  No
  * counterpart in the reference, which has no multi-GPU code.
  *

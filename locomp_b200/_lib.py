@@ -32,6 +32,14 @@ SIGNATURES = {
     "lcq_matmul_select_algo": (_c.c_int, [_c.c_int] * 8),
     "lcq_matmul_int4_noalloc": (_c.c_int, [_c.c_void_p] * 4 + [_c.c_int] * 7 + [_c.c_void_p]),
     "lcq_noalloc_scratch_bytes": (_c.c_size_t, []),
+    "lcq_rms_norm": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int64, _c.c_int, _c.c_float, _c.c_int, _c.c_void_p]),
+    "lcq_residual_rms_norm": (_c.c_int, [_c.c_void_p] * 4 + [_c.c_int64, _c.c_int, _c.c_float, _c.c_int, _c.c_void_p]),
+    "lcq_silu_mul": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int64, _c.c_int, _c.c_void_p]),
+    "lcq_add_inplace": (_c.c_int, [_c.c_void_p] * 2 + [_c.c_int64, _c.c_int, _c.c_void_p]),
+    "lcq_embed_lookup": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int64, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p]),
+    "lcq_argmax": (_c.c_int, [_c.c_void_p] * 2 + [_c.c_int64, _c.c_int, _c.c_int, _c.c_void_p]),
+    "lcq_quantize_int4": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int64, _c.c_int64, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p]),
+    "lcq_quantize_int8": (_c.c_int, [_c.c_void_p] * 3 + [_c.c_int64, _c.c_int64, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p]),
     "lcq_peer_alloc": (_c.c_int, [_c.c_size_t, _c.POINTER(_c.c_void_p), _c.c_char_p]),
     "lcq_peer_open": (_c.c_int, [_c.c_char_p, _c.POINTER(_c.c_void_p)]),
     "lcq_peer_close": (_c.c_int, [_c.c_void_p]),

@@ -11,6 +11,8 @@
 #include "gemv_tc.cuh"
 #include "gemm_tc.cuh"
 #include "peer_gather.cuh"
+#include "glue.cuh"
+#include "quantize.cuh"
 
 namespace lcq {
 
@@ -190,7 +192,12 @@ static size_t gemv_tc_workspace_bytes(int M, int N, int K, int sm_count) {
 
 static int select_algo(int wbits, int M, int N, int K, int G, int x_dtype, int scale_dtype, int out_dtype) {
   (void)out_dtype;
-  if (wbits == 4 && M > 16 && gemm_tc::supported(M, N, K, G, x_dtype, scale_dtype)) return LCQ_ALGO_GEMM_TC;
+  // The prefill kernel rounds each dequantised weight to fp16 (relative error 2^-12); summed over
+  // K > 16384 that error alone reaches the 1e-2 absolute output tolerance in a few outputs per
+  // million, so long-K problems with few rows stay on the decode kernel, whose products are exact.
+  const bool long_k_few_rows = K > 16384 && M <= 64;
+  if (wbits == 4 && M > 16 && !long_k_few_rows && gemm_tc::supported(M, N, K, G, x_dtype, scale_dtype))
+    return LCQ_ALGO_GEMM_TC;
   if (wbits == 4 && gemv_tc::supported(M < 16 ? M : 16, N, K, G, x_dtype, scale_dtype)) return LCQ_ALGO_GEMV_TC;
   return LCQ_ALGO_SIMT;
 }
@@ -522,6 +529,98 @@ size_t lcq_peer_region_bytes(size_t bytes_per_rank, int world) {
   return peer::FLAG_BYTES + bytes_per_rank * static_cast<size_t>(world);
 }
 
+// ---------------------------------------------------------------- decode-step glue, embedding, argmax
+#define LCQ_BY_DTYPE(dtype, CALL)                                   \
+  switch (dtype) {                                                  \
+    case LCQ_F32: { typedef float T; return CALL; }                 \
+    case LCQ_F16: { typedef __half T; return CALL; }                \
+    case LCQ_BF16: { typedef __nv_bfloat16 T; return CALL; }        \
+    default: set_error("bad dtype code %d", dtype); return LCQ_ERR_BAD_ARG; \
+  }
+
+int lcq_rms_norm(const void* x, const void* weight, void* out, int64_t rows, int n, float eps, int dtype, void* stream) {
+  if (rows < 0 || n < 0) { set_error("rms_norm: negative size"); return LCQ_ERR_BAD_ARG; }
+  if (rows == 0 || n == 0) return LCQ_OK;
+  if (!x || !weight || !out) { set_error("null pointer argument"); return LCQ_ERR_BAD_ARG; }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  LCQ_BY_DTYPE(dtype, (glue::launch_rms_norm<T>(x, nullptr, weight, out, rows, n, eps, st)))
+}
+
+int lcq_residual_rms_norm(void* hidden, const void* delta, const void* weight, void* out, int64_t rows, int n, float eps,
+                          int dtype, void* stream) {
+  if (rows < 0 || n < 0) { set_error("residual_rms_norm: negative size"); return LCQ_ERR_BAD_ARG; }
+  if (rows == 0 || n == 0) return LCQ_OK;
+  if (!hidden || !delta || !weight || !out) { set_error("null pointer argument"); return LCQ_ERR_BAD_ARG; }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  LCQ_BY_DTYPE(dtype, (glue::launch_rms_norm<T>(delta, hidden, weight, out, rows, n, eps, st)))
+}
+
+int lcq_silu_mul(const void* gate, const void* up, void* out, int64_t n, int dtype, void* stream) {
+  if (n < 0) { set_error("silu_mul: negative size"); return LCQ_ERR_BAD_ARG; }
+  if (n == 0) return LCQ_OK;
+  if (!gate || !up || !out) { set_error("null pointer argument"); return LCQ_ERR_BAD_ARG; }
+  DevInfo di;
+  int rc = current_dev_info(di);
+  if (rc != LCQ_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  LCQ_BY_DTYPE(dtype, (glue::launch_elementwise<T, 0>(gate, up, out, n, di.sm_count, st)))
+}
+
+int lcq_add_inplace(void* a, const void* b, int64_t n, int dtype, void* stream) {
+  if (n < 0) { set_error("add_inplace: negative size"); return LCQ_ERR_BAD_ARG; }
+  if (n == 0) return LCQ_OK;
+  if (!a || !b) { set_error("null pointer argument"); return LCQ_ERR_BAD_ARG; }
+  DevInfo di;
+  int rc = current_dev_info(di);
+  if (rc != LCQ_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  LCQ_BY_DTYPE(dtype, (glue::launch_elementwise<T, 1>(a, b, a, n, di.sm_count, st)))
+}
+
+int lcq_embed_lookup(const void* token_ids, const void* table, void* out, int64_t tokens, int vocab, int dim, int dtype,
+                     void* stream) {
+  if (tokens < 0 || vocab <= 0 || dim < 0 || !dtype_ok(dtype)) { set_error("embed_lookup: bad size or dtype"); return LCQ_ERR_BAD_ARG; }
+  if (tokens == 0 || dim == 0) return LCQ_OK;
+  if (!token_ids || !table || !out) { set_error("null pointer argument"); return LCQ_ERR_BAD_ARG; }
+  const long long row_bytes = static_cast<long long>(dim) * (dtype == LCQ_F32 ? 4 : 2);
+  return glue::launch_embed(token_ids, table, out, tokens, vocab, row_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int lcq_argmax(const void* x, void* out, int64_t rows, int n, int dtype, void* stream) {
+  if (rows < 0) { set_error("argmax: negative size"); return LCQ_ERR_BAD_ARG; }
+  if (rows == 0) return LCQ_OK;
+  if (!x || !out) { set_error("null pointer argument"); return LCQ_ERR_BAD_ARG; }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  LCQ_BY_DTYPE(dtype, (glue::launch_argmax<T>(x, out, rows, n, st)))
+}
+
+// ---------------------------------------------------------------- quantisers
+static int quantize_entry(int wbits, const void* w, void* q, void* scales, int64_t N, int64_t K, int G, int w_dtype,
+                          int style, void* stream) {
+  int rc = check_problem(wbits, 1, N, K, G);
+  if (rc != LCQ_OK) return rc;
+  if (wbits == 4 && (G % 2) != 0) { set_error("int4 quantiser needs an even group_size, got %d", G); return LCQ_ERR_BAD_ARG; }
+  if (style != 0 && style != 1) { set_error("quantiser style must be 0 or 1, got %d", style); return LCQ_ERR_BAD_ARG; }
+  if (N == 0) return LCQ_OK;
+  if (!w || !q || !scales) { set_error("null pointer argument"); return LCQ_ERR_BAD_ARG; }
+  DevInfo di;
+  rc = current_dev_info(di);
+  if (rc != LCQ_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (wbits == 4) { LCQ_BY_DTYPE(w_dtype, (quant::launch_quantize<T, 4>(w, q, scales, N, K, G, style, di.sm_count, st))) }
+  LCQ_BY_DTYPE(w_dtype, (quant::launch_quantize<T, 8>(w, q, scales, N, K, G, style, di.sm_count, st)))
+}
+
+int lcq_quantize_int4(const void* w, void* w_packed, void* scales, int64_t N, int64_t K, int group_size, int w_dtype,
+                      int style, void* stream) {
+  return quantize_entry(4, w, w_packed, scales, N, K, group_size, w_dtype, style, stream);
+}
+
+int lcq_quantize_int8(const void* w, void* w_int8, void* scales, int64_t N, int64_t K, int group_size, int w_dtype,
+                      int style, void* stream) {
+  return quantize_entry(8, w, w_int8, scales, N, K, group_size, w_dtype, style, stream);
+}
+
 int lcq_set_wait_limit_ns(unsigned long long limit_ns) {
   if (limit_ns == 0) { set_error("lcq_set_wait_limit_ns: the limit must be positive"); return LCQ_ERR_BAD_ARG; }
   LCQ_CUDA_TRY(cudaMemcpyToSymbol(g_wait_limit_ns, &limit_ns, sizeof(limit_ns)));
@@ -535,7 +634,8 @@ int lcq_check_device_status(void* stream) {
   if (v != 0) {
     const int zero = 0;
     LCQ_CUDA_TRY(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
-    set_error("a kernel gave up a bounded wait (code %d)", v);
+    if (v == 40) set_error("a kernel reported a failure (code 40): embed_lookup met a token id outside the table");
+    else set_error("a kernel gave up a bounded wait (code %d)", v);
     return LCQ_ERR_TIMEOUT;
   }
   return LCQ_OK;

@@ -100,6 +100,45 @@ def main(ref_root: str) -> None:
     path = os.path.join(HERE, "reference_vectors.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes")
+    glue_vectors(ref_root)
+
+
+def glue_vectors(ref_root: str) -> None:
+    """Second fixture file: the reference's NumPy forms of the decode-step operators next to the
+    quantized linears (examples/29_rms_norm.py:60-63, examples/31_fused_silu.py:29-31,
+    examples/34_fused_residual_norm.py:63-68) at the SmolLM2-135M widths, and the scales of the
+    examples/52 packer.  Every output stored is an OUTPUT OF REFERENCE CODE on seeded inputs."""
+    ex29 = _load(ref_root, "examples/29_rms_norm.py", "ref_ex29")
+    ex31 = _load(ref_root, "examples/31_fused_silu.py", "ref_ex31")
+    ex34 = _load(ref_root, "examples/34_fused_residual_norm.py", "ref_ex34")
+    ex52 = _load(ref_root, "examples/52_dequantize.py", "ref_ex52_b")
+    out = {}
+    rng = np.random.default_rng(54)
+    for rows, n in [(1, 576), (4, 576), (3, 1000)]:
+        x = rng.standard_normal((rows, n)).astype(np.float32)
+        w = (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+        r = rng.standard_normal((rows, n)).astype(np.float32)
+        tag = f"{rows}x{n}"
+        out[f"norm_{tag}_x"], out[f"norm_{tag}_w"], out[f"norm_{tag}_r"] = x, w, r
+        out[f"norm_{tag}_expected"] = ex29.rms_norm_np(x, w, eps=1e-5)
+        h, normed = ex34.fused_residual_rms_norm_np(r, x, w, eps=1e-5)
+        out[f"resnorm_{tag}_h"], out[f"resnorm_{tag}_expected"] = h, normed
+    for n in (1536, 1000):
+        g = (3.0 * rng.standard_normal(n)).astype(np.float32)
+        u = rng.standard_normal(n).astype(np.float32)
+        out[f"silu_{n}_gate"], out[f"silu_{n}_up"] = g, u
+        out[f"silu_{n}_expected"] = ex31.silu_mul_np(g, u)
+    np.random.seed(42)
+    for tag, n, k, g in [("a", 256, 256, 32), ("d", 24, 96, 16)]:
+        wf = np.random.randn(n, k).astype(np.float32) * 0.1
+        if tag == "d":
+            wf[3, 16:32] = 0.0                      # an all-zero group: the floor at 1e-10 decides its scale
+            wf[5] *= 1e-4                           # small scales: the + 1e-10 in the divisor changes bits
+        p, s = ex52.quantize_int4_ref(wf, g)
+        out[f"q52_{tag}_wf"], out[f"q52_{tag}_g"], out[f"q52_{tag}_p"], out[f"q52_{tag}_s"] = wf, np.int64(g), p, s
+    path = os.path.join(HERE, "glue_vectors.npz")
+    np.savez_compressed(path, **out)
+    print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes")
 
 
 if __name__ == "__main__":

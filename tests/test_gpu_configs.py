@@ -133,7 +133,8 @@ def test_70b_class_shapes_fp16(k, n, m):
     """(K, N) of the column-sharded configuration unsharded, plus the eighth of the vocabulary
     projection (N = 16032, not a multiple of the 128-row tile).  M = 1 and 16 go through the
     decode kernel -- K = 28672 is its longest float32 group-sum chain and most k ranges --,
-    M = 64 through the tcgen05 kernel."""
+    M = 64 through the tcgen05 kernel, except at K = 28672, where AUTO keeps the decode kernel in
+    16-row chunks (the fp16 weight tiles of the tcgen05 kernel are not accurate enough there)."""
     _, _, _, _, rng = _weights(k, n)
     xs = getattr(test_70b_class_shapes_fp16, "_x", {})
     if (k, n) not in xs:                       # one activation draw per shape; M rows are its first M
@@ -141,7 +142,8 @@ def test_70b_class_shapes_fp16(k, n, m):
         xs[(k, n)] = rng.standard_normal((64, k)).astype(np.float16)
         test_70b_class_shapes_fp16._x = xs
     x = np.ascontiguousarray(xs[(k, n)][:m])
-    _run_case(k, n, m, x.astype(np.float32), torch.from_numpy(x).cuda(), "gemv_tc" if m <= 16 else "gemm_tc", seed=m + n)
+    _run_case(k, n, m, x.astype(np.float32), torch.from_numpy(x).cuda(),
+              "gemv_tc" if (m <= 16 or k > 16384) else "gemm_tc", seed=m + n)
 
 
 # --------------------------------------------------------------------------- SmolLM2-135M decode shapes

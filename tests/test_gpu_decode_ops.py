@@ -1,0 +1,214 @@
+"""Parity of the decode-step kernels next to the quantized linears (RMS norm, SiLU*up, residual
+add, embedding lookup, argmax) and of the device quantisers, through the C ABI.
+
+Bars: quantiser outputs (packed bytes and float32 scales) bit-identical to the reference's; copies
+(embedding) and integer results (argmax) exact; float32 norm / activation within 1e-5 relative of
+the float64 oracle and of the reference's NumPy outputs; fp16/bf16 storage within one rounding of
+the output type (rtol 2^-10 / 2^-7) of the oracle evaluated on the same 16-bit inputs.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import locomp_b200 as L
+from locomp_b200 import _lib
+from oracle import decode_oracle as D
+from oracle import qmm_oracle as O
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.fixture(scope="module")
+def glue():
+    return dict(np.load(os.path.join(HERE, "golden", "glue_vectors.npz")))
+
+
+def _status_ok():
+    assert _lib.lib().lcq_check_device_status(None) == 0, _lib.lib().lcq_last_error()
+
+
+# --------------------------------------------------------------------------- norms
+@pytest.mark.parametrize("tag", ["1x576", "4x576", "3x1000"])
+def test_rms_norm_f32_against_reference_outputs(glue, tag):
+    x, w, r = glue[f"norm_{tag}_x"], glue[f"norm_{tag}_w"], glue[f"norm_{tag}_r"]
+    got = L.rms_norm(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), 1e-5).cpu().numpy()
+    np.testing.assert_allclose(got, glue[f"norm_{tag}_expected"], rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(got, D.rms_norm(x, w, 1e-5), rtol=1e-5, atol=1e-6)
+    # residual add + norm in one launch: hidden is updated in place
+    hidden = torch.from_numpy(r.copy()).cuda()
+    normed = L.residual_rms_norm(hidden, torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), 1e-5)
+    assert np.array_equal(hidden.cpu().numpy(), glue[f"resnorm_{tag}_h"])
+    np.testing.assert_allclose(normed.cpu().numpy(), glue[f"resnorm_{tag}_expected"], rtol=1e-5, atol=1e-6)
+    _status_ok()
+
+
+def test_rms_norm_kernel_object_form_and_host_arrays(glue):
+    x, w = glue["norm_4x576_x"], glue["norm_4x576_w"]
+    X, W, Out = L.tensor(x.reshape(-1)), L.tensor(w), L.empty(4 * 576)
+    L.rms_norm_kernel[(4,), (128,)](X, W, Out, 576, int(1e-5 * 1000000))
+    np.testing.assert_allclose(Out.numpy().reshape(4, 576), glue["norm_4x576_expected"], rtol=1e-5, atol=1e-6)
+    out = np.empty_like(x)
+    L.rms_norm(x, w, 1e-5, out=out)                         # host arrays in, host array out
+    np.testing.assert_allclose(out, glue["norm_4x576_expected"], rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("dt,rtol", [(torch.float16, 2.0 ** -10), (torch.bfloat16, 2.0 ** -7)])
+@pytest.mark.parametrize("rows,n", [(1, 576), (5, 1536), (2, 333)])
+def test_norm_and_activation_16bit(dt, rtol, rows, n):
+    g = torch.Generator().manual_seed(rows * n)
+    x = torch.randn(rows, n, generator=g).to(dt)
+    w = (1 + 0.1 * torch.randn(n, generator=g)).to(dt)
+    r = torch.randn(rows, n, generator=g).to(dt)
+    got = L.rms_norm(x.cuda(), w.cuda(), 1e-5)
+    assert got.dtype == dt
+    np.testing.assert_allclose(got.float().cpu().numpy(), D.rms_norm(x.float().numpy(), w.float().numpy(), 1e-5),
+                               rtol=rtol, atol=1e-6)
+    hidden = r.clone().cuda()
+    normed = L.residual_rms_norm(hidden, x.cuda(), w.cuda(), 1e-5)
+    h_ref = (r.float() + x.float()).to(dt)                  # one rounding into the storage type
+    assert torch.equal(hidden.cpu(), h_ref)
+    np.testing.assert_allclose(normed.float().cpu().numpy(), D.rms_norm(h_ref.float().numpy(), w.float().numpy(), 1e-5),
+                               rtol=rtol, atol=1e-6)
+    u = torch.randn(rows, n, generator=g).to(dt)
+    sm = L.silu_mul((3 * x).to(dt).cuda(), u.cuda())
+    np.testing.assert_allclose(sm.float().cpu().numpy(), D.silu_mul((3 * x).to(dt).float().numpy(), u.float().numpy()),
+                               rtol=rtol, atol=1e-6)
+    a = r.clone().cuda()
+    L.add_inplace(a, x.cuda())
+    assert torch.equal(a.cpu(), h_ref)
+    _status_ok()
+
+
+@pytest.mark.parametrize("n", [1536, 1000])
+def test_silu_mul_f32_against_reference_outputs(glue, n):
+    g, u = glue[f"silu_{n}_gate"], glue[f"silu_{n}_up"]
+    got = L.silu_mul(torch.from_numpy(g).cuda(), torch.from_numpy(u).cuda()).cpu().numpy()
+    np.testing.assert_allclose(got, glue[f"silu_{n}_expected"], rtol=1e-5, atol=1e-6)
+    G, U, Out = L.tensor(g), L.tensor(u), L.empty(n)
+    L.silu_mul_kernel[(n,)](G, U, Out, n)
+    np.testing.assert_allclose(Out.numpy(), glue[f"silu_{n}_expected"], rtol=1e-5, atol=1e-6)
+    A, B = L.tensor(g), L.tensor(u)
+    L.add_inplace_kernel[(n,)](A, B, n)
+    assert np.array_equal(A.numpy(), g + u)
+    _status_ok()
+
+
+def test_empty_inputs_are_accepted():
+    e = torch.empty(0, 576, device="cuda")
+    assert L.rms_norm(e, torch.ones(576, device="cuda")).shape == (0, 576)
+    assert L.silu_mul(torch.empty(0, device="cuda"), torch.empty(0, device="cuda")).numel() == 0
+
+
+# --------------------------------------------------------------------------- embedding + argmax
+@pytest.mark.parametrize("dt", [torch.float32, torch.float16])
+@pytest.mark.parametrize("dim", [576, 50])
+def test_embed_lookup_is_an_exact_copy(dt, dim):
+    vocab, seq = 1000, 7
+    g = torch.Generator().manual_seed(dim)
+    table = torch.randn(vocab, dim, generator=g).to(dt)
+    ids = torch.tensor([0, 999, 5, 5, 123, 998, 1], dtype=torch.int32)
+    out = torch.zeros(seq * dim, dtype=dt, device="cuda")
+    L.embed_lookup(ids.cuda(), table.cuda(), out, seq_len=seq, dim=dim)
+    exp = D.embed_lookup(ids.numpy(), table.numpy() if dt != torch.bfloat16 else table.float().numpy())
+    assert np.array_equal(out.cpu().numpy().reshape(seq, dim), exp)
+    _status_ok()
+
+
+def test_embed_lookup_reports_an_id_out_of_range():
+    table = torch.ones(10, 16, device="cuda")
+    out = torch.full((2 * 16,), 7.0, device="cuda")
+    L.embed_lookup(torch.tensor([3, 10], dtype=torch.int32).cuda(), table, out, 2, 16)
+    assert _lib.lib().lcq_check_device_status(None) == _lib.ERR_TIMEOUT      # code 40 in the status word
+    assert b"code 40" in _lib.lib().lcq_last_error()
+    assert _lib.lib().lcq_check_device_status(None) == 0
+    assert torch.equal(out[:16].cpu(), torch.ones(16)) and torch.equal(out[16:].cpu(), torch.zeros(16))
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.float32, torch.bfloat16])
+def test_argmax_matches_numpy_on_seeded_cases(dt):
+    """100 seeded rows of vocabulary width incl. ties (coarse 16-bit logits), plus ragged widths."""
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(100, 49152, generator=g).to(dt)
+    x[3, 100] = x[3].max()
+    x[3, 40000] = x[3].max()                                  # an exact tie: the lower index wins
+    got = L.argmax(x.cuda())
+    assert got.dtype == torch.int32
+    assert np.array_equal(got.cpu().numpy(), D.argmax(x.float().numpy()))
+    for n in (1, 7, 1000, 4099):
+        y = torch.randn(3, n, generator=g).to(dt)
+        assert np.array_equal(L.argmax(y.cuda()).cpu().numpy(), D.argmax(y.float().numpy()))
+    v = torch.tensor([1.0, float("nan"), 5.0, float("nan")])
+    assert int(L.argmax(v.cuda())) == int(np.argmax(v.numpy())) == 1
+    _status_ok()
+
+
+def test_lm_head_argmax_equals_argmax_of_the_kernels_own_logits():
+    """Greedy token on the device: argmax of the fp16 logits the lm_head kernel produced."""
+    rng = np.random.default_rng(3)
+    wp, s = O.make_w4(rng, 49152, 576, 32, np.float16)
+    wd, sd = torch.from_numpy(wp).cuda(), torch.from_numpy(s).cuda()
+    for i in range(20):
+        x = torch.from_numpy(rng.standard_normal((1, 576)).astype(np.float16)).cuda()
+        logits = L.quantized_matmul(x, wd, sd, 32)
+        tok = L.argmax(logits)
+        assert int(tok[0]) == int(np.argmax(logits.float().cpu().numpy()[0]))
+    _status_ok()
+
+
+# --------------------------------------------------------------------------- quantisers
+@pytest.mark.parametrize("tag", ["a", "b", "c", "d"])
+def test_quantisers_bit_identical_to_reference(golden, tag):
+    wf, g = golden[f"mv_{tag}_wf"], int(golden[f"mv_{tag}_g"])
+    p4, s4 = L.quantize_int4(wf, g)
+    assert p4.dtype == np.uint8 and s4.dtype == np.float32
+    assert np.array_equal(p4, golden[f"mv_{tag}_p4"])
+    assert np.array_equal(s4.view(np.uint32), golden[f"mv_{tag}_s4"].view(np.uint32))
+    w8, s8 = L.quantize_int8(wf, g)
+    assert w8.dtype == np.int8
+    assert np.array_equal(w8, golden[f"mv_{tag}_w8"])
+    assert np.array_equal(s8.view(np.uint32), golden[f"mv_{tag}_s8"].view(np.uint32))
+    p52, _ = L.quantize_int4_ref(wf, g)
+    assert np.array_equal(p52, golden[f"mv_{tag}_p4_ex52"])
+
+
+@pytest.mark.parametrize("tag", ["a", "d"])
+def test_ex52_quantiser_bit_identical_incl_zero_groups(glue, tag):
+    p, s = L.quantize_int4_ref(glue[f"q52_{tag}_wf"], int(glue[f"q52_{tag}_g"]))
+    assert np.array_equal(p, glue[f"q52_{tag}_p"])
+    assert np.array_equal(s.view(np.uint32), glue[f"q52_{tag}_s"].view(np.uint32))
+
+
+@pytest.mark.parametrize("n,k,g", [(4096, 4096, 32), (64, 120, 12), (33, 512, 256), (7, 96, 6)])
+def test_quantiser_against_oracle_large_and_odd_groups(n, k, g):
+    rng = np.random.default_rng(n + k)
+    w = (rng.standard_normal((n, k)) * 0.1).astype(np.float32)
+    w[0, :g] = 0.0                                            # an all-zero group -> scale 1.0
+    qw = L.quantize(torch.from_numpy(w).cuda(), g, bits=4)
+    p_ref, s_ref = O.quantize_int4(w, g)
+    assert np.array_equal(qw.w.cpu().numpy(), p_ref)
+    assert np.array_equal(qw.scales.cpu().numpy().view(np.uint32), s_ref.view(np.uint32))
+    q8 = L.quantize(torch.from_numpy(w).cuda(), g, bits=8)
+    w8_ref, s8_ref = O.quantize_int8(w, g)
+    assert np.array_equal(q8.w.cpu().numpy(), w8_ref)
+    assert np.array_equal(q8.scales.cpu().numpy().view(np.uint32), s8_ref.view(np.uint32))
+    _status_ok()
+
+
+def test_quantize_then_matmul_round_trip(tmp_path):
+    """Quantise on the device, keep the container, run the linear: equals the oracle on the
+    reference-quantised weight; the container survives save / load."""
+    rng = np.random.default_rng(11)
+    w = (rng.standard_normal((512, 1024)) * 0.1).astype(np.float32)
+    qw = L.quantize(torch.from_numpy(w).cuda(), 32, bits=4, scale_dtype="f16")
+    assert qw.shape == (512, 1024) and qw.scales.dtype == torch.float16
+    x = rng.standard_normal((2, 1024)).astype(np.float16)
+    y = qw.linear()(torch.from_numpy(x).cuda())
+    p_ref, s_ref = O.quantize_int4(w, 32)
+    ref = O.matmul_int4(x.astype(np.float32), p_ref, s_ref.astype(np.float16), 32)
+    assert np.all(np.abs(y.float().cpu().numpy() - ref) <= 1e-2 + 1e-2 * np.abs(ref))
+    qw.save(str(tmp_path / "w.npz"))
+    back = L.QuantizedWeight.load(str(tmp_path / "w.npz"))
+    assert torch.equal(back.w, qw.w) and torch.equal(back.scales, qw.scales) and back.group_size == 32 and back.bits == 4

@@ -99,3 +99,36 @@ def test_ragged_and_empty():
         O.dequant_int4(wp, s, 48)
     with pytest.raises(ValueError):
         O.dequant_int4(wp.astype(np.int8), s, 32)
+
+
+# --------------------------------------------------------------------------- decode-step operators
+@pytest.fixture(scope="module")
+def glue():
+    import os
+    here = os.path.dirname(os.path.abspath(__file__))
+    return dict(np.load(os.path.join(here, "golden", "glue_vectors.npz")))
+
+
+@pytest.mark.parametrize("tag", ["1x576", "4x576", "3x1000"])
+def test_decode_oracle_norms_match_reference_numpy_forms(glue, tag):
+    from oracle import decode_oracle as D
+    x, w, r = glue[f"norm_{tag}_x"], glue[f"norm_{tag}_w"], glue[f"norm_{tag}_r"]
+    np.testing.assert_allclose(D.rms_norm(x, w, 1e-5), glue[f"norm_{tag}_expected"], rtol=2e-6, atol=1e-7)
+    h, normed = D.residual_rms_norm(r, x, w, 1e-5)
+    assert np.array_equal(h, glue[f"resnorm_{tag}_h"])                 # one float32 addition: exact
+    np.testing.assert_allclose(normed, glue[f"resnorm_{tag}_expected"], rtol=2e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("n", [1536, 1000])
+def test_decode_oracle_silu_matches_reference_numpy_form(glue, n):
+    from oracle import decode_oracle as D
+    np.testing.assert_allclose(D.silu_mul(glue[f"silu_{n}_gate"], glue[f"silu_{n}_up"]), glue[f"silu_{n}_expected"],
+                               rtol=2e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("tag", ["a", "d"])
+def test_ex52_quantiser_oracle_bit_exact(glue, tag):
+    from oracle import decode_oracle as D
+    p, s = D.quantize_int4_ex52(glue[f"q52_{tag}_wf"], int(glue[f"q52_{tag}_g"]))
+    assert np.array_equal(p, glue[f"q52_{tag}_p"])
+    assert np.array_equal(s.view(np.uint32), glue[f"q52_{tag}_s"].view(np.uint32))
