@@ -115,7 +115,7 @@ int lcq_matmul_select_algo(int wbits, int M, int N, int K, int group_size,
  * Decode matmul that allocates nothing.  No counterpart in the reference.
  *
  * Same computation and same kernel as lcq_matmul_int4 with LCQ_ALGO_GEMV_TC (M <= 16,
- * group_size 32, K % 256 == 0, f16 scales, f16/bf16 x), but the split-K scratch is a fixed array
+ * group_size 32, K % 64 == 0, f16 scales, f16/bf16 x), but the split-K scratch is a fixed array
  * inside the library instead of a caller-provided workspace.  It exists for callers that cannot
  * obtain device memory at the point of the call: a serving loop whose framework has taken the
  * whole device into its own pool (so cudaMalloc fails or is forbidden), or a host that must not

@@ -12,12 +12,15 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
-LIB_PATH = os.path.join(PKG_DIR, "_lcq.so")
+# LOCOMP_B200_LIB selects another build of the library (e.g. one compiled with different tuning macros)
+LIB_PATH = os.environ.get("LOCOMP_B200_LIB") or os.path.join(PKG_DIR, "_lcq.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
     "-shared", "-Xcompiler", "-fPIC",
+    # a host-only constexpr function called from device code compiles to a trap: make that an error
+    "-Werror", "cross-execution-space-call",
 ]
 
 

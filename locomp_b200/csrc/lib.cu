@@ -228,7 +228,7 @@ static int matmul_entry(int wbits, const void* x, const void* w, const void* s, 
                         : simt_entry<8>(x, w, s, out, M, N, K, G, x_dtype, scale_dtype, out_dtype, st);
     case LCQ_ALGO_GEMV_TC: {
       if (wbits != 4 || !gemv_tc::supported(M < 16 ? M : 16, N, K, G, x_dtype, scale_dtype)) {
-        set_error("GEMV_TC needs int4, group_size 32, K %% 256 == 0, f16 scales, f16/bf16 x");
+        set_error("GEMV_TC needs int4, group_size 32, K %% 64 == 0, f16 scales, f16/bf16 x");
         return LCQ_ERR_UNSUPPORTED;
       }
       // M > 16: rows of x in chunks of 16 (each chunk re-streams the weights).  Every chunk's plan
@@ -377,6 +377,7 @@ int lcq_gemv_tc_plan_check(int M, int N, int K, int sm_count, int* fields) {
     const gemv_tc::Sched s = gemv_tc::make_sched(p, kr);
     if (j >= s.G) continue;
     const long long t0 = gemv_tc::tile_begin(s, j), t1 = gemv_tc::tile_begin(s, j + 1);
+    if (!pl.fits_32bit) { set_error("plan check: schedule does not fit 32 bits"); return LCQ_ERR_UNSUPPORTED; }
     if (t1 <= t0) { set_error("plan check: CTA %d has no tiles", b); return LCQ_ERR_BAD_ARG; }
     int last_rb = -1;
     for (long long t = t0; t < t1; ++t) {
@@ -439,7 +440,7 @@ int lcq_matmul_int4_noalloc(const void* x, const void* w_packed, const void* sca
   if (M == 0 || N == 0) return LCQ_OK;
   if (!x || !w_packed || !scales || !out) { set_error("null pointer argument"); return LCQ_ERR_BAD_ARG; }
   if (!gemv_tc::supported(M, N, K, group_size, x_dtype, scale_dtype)) {
-    set_error("lcq_matmul_int4_noalloc covers M <= 16, group_size 32, K %% 256 == 0, f16 scales, f16/bf16 x");
+    set_error("lcq_matmul_int4_noalloc covers M <= 16, group_size 32, K %% 64 == 0, f16 scales, f16/bf16 x");
     return LCQ_ERR_UNSUPPORTED;
   }
   DevInfo di;

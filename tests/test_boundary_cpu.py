@@ -67,7 +67,8 @@ def test_algo_selection():
     sel = lib.lcq_matmul_select_algo
     assert sel(4, 1, 2048, 2048, 32, _lib.F16, _lib.F16, _lib.F16) == _lib.ALGO_GEMV_TC
     assert sel(4, 16, 2048, 8192, 32, _lib.F16, _lib.F16, _lib.F16) == _lib.ALGO_GEMV_TC
-    assert sel(4, 1, 1536, 576, 32, _lib.F16, _lib.F16, _lib.F16) == _lib.ALGO_SIMT      # K % 256 != 0
+    assert sel(4, 1, 1536, 576, 32, _lib.F16, _lib.F16, _lib.F16) == _lib.ALGO_GEMV_TC   # K % 256 != 0: partial last k tile
+    assert sel(4, 1, 1536, 96, 32, _lib.F16, _lib.F16, _lib.F16) == _lib.ALGO_SIMT       # K % 64 != 0
     assert sel(4, 1, 4096, 4096, 32, _lib.F32, _lib.F32, _lib.F32) == _lib.ALGO_SIMT     # reference dtypes
     assert sel(8, 1, 1536, 576, 576, _lib.F32, _lib.F32, _lib.F32) == _lib.ALGO_SIMT
     assert lib.lcq_matmul_workspace_bytes(8, 1, 1536, 576, 576, 0, 0, 0, 0) == 0
@@ -79,7 +80,7 @@ def test_gemv_plan_covers_every_tile_once(M):
     lib = _lib.lib()
     f = (ctypes.c_int * 8)()
     for N in (1, 100, 128, 192, 1024, 2048, 8192, 16032, 49152, 128256):
-        for K in (256, 768, 2048, 8192, 28672):
+        for K in (64, 256, 576, 768, 2048, 8192, 28672):
             for sms in (148, 132, 7, 1):
                 rc = lib.lcq_gemv_tc_plan_check(M, N, K, sms, f)
                 assert rc == 0, (M, N, K, sms, lib.lcq_last_error())

@@ -64,5 +64,5 @@ def test_noalloc_rejects_what_does_not_fit():
     # outside the decode kernel's domain
     rc = lib.lcq_matmul_int4_noalloc(one, one, one, one, 64, 1024, 1024, 32, F16, F16, F16, None)
     assert rc == _lib.ERR_UNSUPPORTED
-    rc = lib.lcq_matmul_int4_noalloc(one, one, one, one, 1, 1024, 576, 32, F16, F16, F16, None)
+    rc = lib.lcq_matmul_int4_noalloc(one, one, one, one, 1, 1024, 96, 32, F16, F16, F16, None)
     assert rc == _lib.ERR_UNSUPPORTED
