@@ -46,8 +46,9 @@ extern "C" {
 /* algorithm selector for lcq_matmul_int4/int8 */
 #define LCQ_ALGO_AUTO    0   /* pick by shape and dtype                                         */
 #define LCQ_ALGO_SIMT    1   /* warp-per-row CUDA-core kernel; any K % group_size == 0           */
-#define LCQ_ALGO_GEMV_TC 2   /* M <= 16: TMA-staged int4 stream + warp-level MMA, split-K        */
+#define LCQ_ALGO_GEMV_TC 2   /* int4, M <= 16, K % 64 == 0: TMA-staged int4 stream + warp-level MMA, split-K */
 #define LCQ_ALGO_GEMM_TC 3   /* M >= 17: TMA + in-kernel dequant + tcgen05 MMA, TMEM accumulators */
+#define LCQ_ALGO_GEMV_W8 4   /* int8, M <= 8: TMA-staged int8 stream, 128-bit shared loads, float32 math */
 
 int         lcq_version(void);
 const char* lcq_status_string(int status);

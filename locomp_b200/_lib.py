@@ -12,7 +12,7 @@ from .build import LIB_PATH
 OK = 0
 ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_TIMEOUT = -1, -2, -3, -4, -5
 F32, F16, BF16 = 0, 1, 2
-ALGO_AUTO, ALGO_SIMT, ALGO_GEMV_TC, ALGO_GEMM_TC = 0, 1, 2, 3
+ALGO_AUTO, ALGO_SIMT, ALGO_GEMV_TC, ALGO_GEMM_TC, ALGO_GEMV_W8 = 0, 1, 2, 3, 4
 
 # name -> (restype, argtypes); mirrors include/locomp_b200.h one to one
 _c = ctypes

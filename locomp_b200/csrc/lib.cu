@@ -9,6 +9,7 @@
 #include "dequant.cuh"
 #include "gemv_simt.cuh"
 #include "gemv_tc.cuh"
+#include "gemv_w8.cuh"
 #include "gemm_tc.cuh"
 #include "peer_gather.cuh"
 #include "glue.cuh"
@@ -199,6 +200,7 @@ static int select_algo(int wbits, int M, int N, int K, int G, int x_dtype, int s
   if (wbits == 4 && M > 16 && !long_k_few_rows && gemm_tc::supported(M, N, K, G, x_dtype, scale_dtype))
     return LCQ_ALGO_GEMM_TC;
   if (wbits == 4 && gemv_tc::supported(M < 16 ? M : 16, N, K, G, x_dtype, scale_dtype)) return LCQ_ALGO_GEMV_TC;
+  if (wbits == 8 && gemv_w8::supported(M, N, K, G)) return LCQ_ALGO_GEMV_W8;
   return LCQ_ALGO_SIMT;
 }
 
@@ -251,6 +253,16 @@ static int matmul_entry(int wbits, const void* x, const void* w, const void* s, 
       }
       return LCQ_OK;
     }
+    case LCQ_ALGO_GEMV_W8:
+      if (wbits != 8 || !gemv_w8::supported(M, N, K, G)) {
+        set_error("GEMV_W8 needs int8 weights, M <= 8, K %% 16 == 0, group_size %% 16 == 0");
+        return LCQ_ERR_UNSUPPORTED;
+      }
+      switch (x_dtype) {
+        case LCQ_F32: return gemv_w8::launch<float>(x, w, s, out, M, N, K, G, scale_dtype, out_dtype, st);
+        case LCQ_F16: return gemv_w8::launch<__half>(x, w, s, out, M, N, K, G, scale_dtype, out_dtype, st);
+        default: return gemv_w8::launch<__nv_bfloat16>(x, w, s, out, M, N, K, G, scale_dtype, out_dtype, st);
+      }
     case LCQ_ALGO_GEMM_TC:
       if (wbits != 4 || !gemm_tc::supported(M, N, K, G, x_dtype, scale_dtype)) {
         set_error("GEMM_TC needs int4, group_size 32, K %% 256 == 0, f16 scales, f16/bf16 x");
@@ -335,6 +347,7 @@ size_t lcq_matmul_workspace_bytes(int wbits, int M, int N, int K, int group_size
   if (M == 0 || N == 0) return 0;
   if (algo == LCQ_ALGO_AUTO) algo = select_algo(wbits, M, N, K, group_size, x_dtype, scale_dtype, out_dtype);
   if (algo == LCQ_ALGO_SIMT) return 0;
+  if (algo == LCQ_ALGO_GEMV_W8) return (wbits == 8 && gemv_w8::supported(M, N, K, group_size)) ? 0 : static_cast<size_t>(-1);
   int sm = 148;  // B200; refined from the device when one is present
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) {

@@ -28,7 +28,7 @@ from .tensor import (KIND_TO_CODE, KIND_TO_TORCH, DeviceTensor, Operand, _requir
                      resolve, workspace)
 
 _ALGOS = {None: _lib.ALGO_AUTO, "auto": _lib.ALGO_AUTO, "simt": _lib.ALGO_SIMT,
-          "gemv_tc": _lib.ALGO_GEMV_TC, "gemm_tc": _lib.ALGO_GEMM_TC}
+          "gemv_tc": _lib.ALGO_GEMV_TC, "gemm_tc": _lib.ALGO_GEMM_TC, "gemv_w8": _lib.ALGO_GEMV_W8}
 
 
 def _float_kind(op: Operand, name: str) -> int:
