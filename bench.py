@@ -14,6 +14,11 @@ of every linear -- the shard has the cfg2 shape, so per-GPU work is fixed (weak 
 global linear is N times wider -- and the outputs are reassembled with an NCCL all-gather inside
 the timed region.
 
+The same JSON line carries one block per other configuration (bench_blocks.py): "cfg1" (int8
+matvec), "cfg3" (decode stack, microseconds per token), "cfg4" (prefill GEMM TFLOP/s), "cfg5"
+(70B-class shapes split along N over the ranks: compute-only and compute+gather), "dequant", and
+"e2e_resident" (weights resident, x up / y down per call).
+
 --impl reference times the reference's CPU path (the NumPy dequantise-then-BLAS matvec of
 examples/38_quantized_matmul.py:215-232, restated in oracle/qmm_oracle.py) on the host cores.
 """
@@ -44,9 +49,6 @@ CFG3_LM_HEAD = (576, 49152)
 CFG5_SHAPES = [(8192, 28672), (28672, 8192), (8192, 128256)]
 CFG5_MS = [1, 16, 64]
 GROUP = 32
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
-# profiles/ (bytes), keyed by (K, N, M)
-TRAFFIC_NCU = {(2048, 49152, 1): 56681216 + 28672}
 
 
 def weight_bytes(k: int, n: int) -> int:
@@ -383,19 +385,31 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             sampler.start()      # one NVML query takes milliseconds: sample from the warm-up on, through the timed region
         for i in range(args.warmup):
             step(i)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for i in range(args.steps):
-            step(args.warmup + i)
-        e1.record(stream)
-        barrier()
+        # The timed region is exactly `steps` steps between a barrier + synchronize on both sides; it
+        # is repeated until the repeats span about half a second, and the median repeat is reported.
+        region_ms = []
+        it = args.warmup
+        budget_ms, spent_ms = 500.0, 0.0
+        while True:
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(args.steps):
+                step(it + i)
+            e1.record(stream)
+            barrier()
+            it += args.steps
+            reg = e0.elapsed_time(e1)
+            if dist is not None:
+                t = torch.tensor([reg], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                reg = float(t.item())
+            region_ms.append(reg)
+            spent_ms += reg
+            if spent_ms >= budget_ms or len(region_ms) >= 200:
+                break
         clocks = sampler.stop() if rank == 0 else None
-    ms_total = e0.elapsed_time(e1)
-    if dist is not None:
-        t = torch.tensor([ms_total], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
+    ms_total = statistics.median(region_ms)
     _lib.check(lib.lcq_check_device_status(None))
 
     total_bytes = per_set_bytes * world * args.steps
@@ -420,86 +434,25 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "launch": graph_note,
             "sharding": None if world == 1 else (f"N-column shards + " + ("NVLink peer-store all-gather kernel" if peer is not None else "NCCL all-gather") + f", {world} ranks"),
         },
-        "gpu_launches": args.steps * len(shapes) * len(ms),
+        "gpu_launches": args.steps * len(shapes) * len(ms) * len(region_ms),
+        "timed_regions": {"count": len(region_ms), "steps_each": args.steps, "ms_median": ms_total, "ms_min": min(region_ms),
+                          "ms_max": max(region_ms), "reported": "median"},
         "weight_bytes_per_step": per_set_bytes * world,
     }
     if args.workload == "cfg3":
         line["us_per_token"] = ms_total / args.steps * 1e3
-        if rank == 0 and world == 1:
-            # same weights' worth of work with q|k|v and gate|up fused into one launch each
-            # (121 launches per token); four stacks rotate so a stack's 76 MB is out of L2 on reuse
-            stacks = [L.DecodeStack(fused=True, seed=100 + i) for i in range(4)]
-            for st in stacks:
-                st.capture()
-            torch.cuda.synchronize()
-            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            for i in range(args.warmup):
-                stacks[i % 4].replay()
-            f0.record()
-            for i in range(args.steps):
-                stacks[i % 4].replay()
-            f1.record()
-            torch.cuda.synchronize()
-            line["us_per_token_fused_qkv_gateup"] = f0.elapsed_time(f1) / args.steps * 1e3
-            del stacks
     if rank == 0:
         line["clocks"] = clocks
+    # ---------------------------------------------------------------- graphs hold NCCL work: drop them before anything else
+    graphs = None
+    import bench_blocks as B
+    ctx = B.Ctx(torch, lib, _lib, L, dev, peaks, rank, world, dist)
     # ---------------------------------------------------------------- roofline of the dominant kernel
-    if rank == 0 and args.workload != "cfg4":
-        # the dominant kernel: the largest shape of the workload at its smallest M, one call per
-        # weight set.  Average launch duration = CUDA events on the launching stream around R
-        # back-to-back launches over rotating weight buffers (R * bytes >> L2), divided by R.
-        big = [calls[-1 if args.workload == "cfg3" else (len(shapes) - 1) * len(ms)] for calls in sets]
-        others = [c for c in sets[0] if c is not big[0]]
-        reps = max(2, int(np.ceil(400e6 / (weight_bytes(big[0].k, big[0].n) * len(big)))))
-        with torch.cuda.stream(stream):
-            for c in big:                       # warm
-                c.launch(sp)
-            for c in others:                    # push the big buffers out of L2
-                c.launch(sp)
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(stream)
-            for rep in range(reps):
-                for c in big:
-                    c.launch(sp)
-            b.record(stream)
-        torch.cuda.synchronize()
-        avg_ms = a.elapsed_time(b) / (reps * len(big))
-        k, n = big[0].k, big[0].n
-        algo = lib.lcq_matmul_select_algo(4, big[0].m, n, k, GROUP, big[0].code, _lib.F16, big[0].code)
-        kname = {_lib.ALGO_SIMT: "gemv_simt_kernel", _lib.ALGO_GEMV_TC: "w4a16_gemv_kernel",
-                 _lib.ALGO_GEMM_TC: "w4a16_gemm_kernel"}.get(algo, "?")
-        achieved = weight_bytes(k, n) / (avg_ms * 1e-3) / 1e9
-        line["roofline"] = {
-            "bound": "hbm", "kernel": f"{kname} M={big[0].m} K={k} N={n}", "achieved": achieved,
-            "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
-            "frac": achieved / peaks["hbm_gbs"], "avg_launch_us": avg_ms * 1e3,
-            "launches_timed": reps * len(big),
-            "algorithmic_bytes_per_launch": weight_bytes(k, n), "traffic": TRAFFIC_NCU.get((k, n, big[0].m)),
-        }
+    if rank == 0 and args.workload in ("cfg2", "cfg3", "cfg5"):
+        k, n = {"cfg2": (2048, 49152), "cfg3": (576, 49152), "cfg5": (8192, 128256 // world)}[args.workload]
+        line["roofline"] = B.block_roofline(ctx, k, n, 1)
     if rank == 0 and args.workload == "cfg4":
-        big = [c for calls in sets for c in calls if c.m == ms[-1] and (c.k, c.n) == shapes[1]]
-        durs = []
-        with torch.cuda.stream(stream):
-            for rep in range(3):
-                for c in big:
-                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a.record(stream)
-                    c.launch(sp)
-                    b.record(stream)
-                    durs.append((a, b))
-        torch.cuda.synchronize()
-        times = [a.elapsed_time(b) for (a, b) in durs][len(big):]
-        avg_ms = sum(times) / len(times)
-        k, n, m = big[0].k, big[0].n, big[0].m
-        achieved = 2.0 * m * n * k / (avg_ms * 1e-3) / 1e12
-        line["roofline"] = {
-            "bound": "tensor", "kernel": f"w4a16_gemm_kernel (+ bf16->f16 pre-pass) M={m} K={k} N={n}",
-            "achieved": achieved, "peak": peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst)",
-            "peak_sustained": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
-            "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"], "avg_launch_us": avg_ms * 1e3,
-            "algorithmic_flops_per_launch": 2.0 * m * n * k, "traffic": None,
-        }
+        line["roofline"] = B.block_cfg4(ctx)["roofline"]
     # ---------------------------------------------------------------- end-to-end through the reference-facing call
     if args.workload == "cfg2":
         host_sets = []
@@ -555,6 +508,19 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "kind": "port",
             "sample": f"(K,N)=(2048,8192), M in {{1,4,16}}, {reps} passes; NumPy dequantise-to-float32 + BLAS "
                       "(oracle.fast_matvec_int4, restating examples/38_quantized_matmul.py:215-232)"}
+    # ---------------------------------------------------------------- the other configurations, one block each
+    if args.workload == "cfg2" and not args.no_extra:
+        for calls in sets:                    # the headline's buffers are no longer needed
+            calls.clear()
+        torch.cuda.empty_cache()
+        line["e2e_resident"] = B.block_e2e_resident(ctx, shapes, ms)
+        line["cfg5"] = B.block_cfg5(ctx, gather=args.gather)        # every rank takes part
+        if rank == 0 and world == 1:
+            line["cfg1"] = B.block_cfg1(ctx)
+            line["cfg3"] = B.block_cfg3(ctx)
+            line["cfg4"] = B.block_cfg4(ctx)
+            line["dequant"] = B.block_dequant(ctx)
+        line["gpu_launches"] += ctx.launches
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
@@ -581,6 +547,7 @@ def main():
     ap.add_argument("--profile-shape", default=None, metavar="KxNxM",
                     help="run a few launches of one problem and exit (small case for ncu captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="headline only: skip the cfg1/cfg3/cfg4/cfg5/dequant blocks")
     args = ap.parse_args()
     if args.watchdog > 0:
         import threading

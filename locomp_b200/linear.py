@@ -59,11 +59,16 @@ class DecodeStack:
     chained on fixed activation buffers: q|k|v, o, gate|up, down per layer, then the lm_head.
     Only the linears run -- attention, norms and activations between them are not part of this
     path -- so every linear reads a prepared activation buffer of its input width.
-    `fused=True` uses one launch for q|k|v and one for gate|up (4 launches per layer instead of 7)."""
+    `fused=True` uses one launch for q|k|v and one for gate|up (4 launches per layer instead of 7).
+    `glue=True` (with fused) also runs what sits between the linears in the reference's layer
+    (examples/54_smollm2_inference.py:494-554, :556-578) except attention itself: embedding lookup,
+    input RMS norm, residual add + post-attention norm (one kernel), SiLU * up, residual add, final
+    norm, and a greedy argmax of the logits on the device -- a real dependency chain on one hidden
+    state, 8 launches per layer."""
 
     def __init__(self, layers: int = 30, hidden: int = 576, inter: int = 1536, q_heads: int = 9, kv_heads: int = 3,
                  head_dim: int = 64, vocab: int = 49152, fused: bool = False, device="cuda", seed: int = 0,
-                 dtype=torch.float16):
+                 dtype=torch.float16, glue: bool = False):
         g = torch.Generator(device=device).manual_seed(seed)
 
         def make(n, k):
@@ -71,6 +76,10 @@ class DecodeStack:
             s = (torch.randn(n, k // 32, device=device, generator=g).abs() * 0.02).to(torch.float16)
             return w, s
         qd, kvd = q_heads * head_dim, kv_heads * head_dim
+        if glue and not fused:
+            raise ValueError("glue=True runs the fused layer form")
+        self.glue = glue
+        self.ops = []                                  # with glue: the step as a list of zero-argument launches
         self.calls: List[Tuple[QuantLinear, torch.Tensor, torch.Tensor]] = []   # (linear, x, out)
         x_h = torch.randn(1, hidden, device=device, generator=g).to(dtype)
         x_i = torch.randn(1, inter, device=device, generator=g).to(dtype)
@@ -78,6 +87,39 @@ class DecodeStack:
 
         def add(lin, x):
             self.calls.append((lin, x, torch.empty(1, lin.out_features, dtype=dtype, device=device)))
+        if glue:
+            from . import decode_ops as D
+            self.table = (torch.randn(vocab, hidden, device=device, generator=g) * 0.02).to(dtype)
+            self.token = torch.zeros(1, dtype=torch.int32, device=device)
+            self.next_token = torch.zeros(1, dtype=torch.int32, device=device)
+            self.hidden = torch.zeros(1, hidden, dtype=dtype, device=device)
+            self.normed = torch.zeros(1, hidden, dtype=dtype, device=device)
+            self.mlp = torch.zeros(1, inter, dtype=dtype, device=device)
+
+            def lin_op(lin, x):
+                out = torch.empty(1, lin.out_features, dtype=dtype, device=device)
+                self.calls.append((lin, x, out))
+                self.ops.append(lambda: lin(x, out=out, workspace_buf=self.workspace))
+                return out
+            self.ops.append(lambda: D.embed_lookup(self.token, self.table, self.hidden, 1, hidden))
+            for _ in range(layers):
+                q, k, v, o = make(qd, hidden), make(kvd, hidden), make(kvd, hidden), make(hidden, qd)
+                gate, up, down = make(inter, hidden), make(inter, hidden), make(hidden, inter)
+                w_in = (1 + 0.1 * torch.randn(hidden, device=device, generator=g)).to(dtype)
+                w_post = (1 + 0.1 * torch.randn(hidden, device=device, generator=g)).to(dtype)
+                self.ops.append(lambda w=w_in: D.rms_norm(self.hidden, w, 1e-5, out=self.normed))
+                lin_op(fuse_rows([q, k, v])[0], self.normed)
+                o_out = lin_op(QuantLinear(*o), x_q)            # attention is not part of this path: o reads a prepared buffer
+                self.ops.append(lambda w=w_post, d=o_out: D.residual_rms_norm(self.hidden, d, w, 1e-5, out=self.normed))
+                gu = lin_op(fuse_rows([gate, up])[0], self.normed)
+                self.ops.append(lambda gu=gu: D.silu_mul(gu[:, :inter], gu[:, inter:], out=self.mlp))
+                d_out = lin_op(QuantLinear(*down), self.mlp)
+                self.ops.append(lambda d=d_out: D.add_inplace(self.hidden, d))
+            w_fin = (1 + 0.1 * torch.randn(hidden, device=device, generator=g)).to(dtype)
+            self.ops.append(lambda: D.rms_norm(self.hidden, w_fin, 1e-5, out=self.normed))
+            self.logits = lin_op(QuantLinear(*make(vocab, hidden)), self.normed)
+            self.ops.append(lambda: D.argmax(self.logits, out=self.next_token))
+            layers = 0                                 # the plain construction below adds nothing more
         for _ in range(layers):
             q, k, v, o = make(qd, hidden), make(kvd, hidden), make(kvd, hidden), make(hidden, qd)
             gate, up, down = make(inter, hidden), make(inter, hidden), make(hidden, inter)
@@ -93,7 +135,9 @@ class DecodeStack:
                 add(QuantLinear(*gate), x_h)
                 add(QuantLinear(*up), x_h)
                 add(QuantLinear(*down), x_i)
-        add(QuantLinear(*make(vocab, hidden)), x_h)
+        if not glue:
+            add(QuantLinear(*make(vocab, hidden)), x_h)
+        self.launches_per_step = len(self.ops) if glue else len(self.calls)
         self.weight_bytes = sum(c[0].weight_bytes for c in self.calls)
         # one scratch buffer for the whole stack (calls are stream-ordered), allocated up front so
         # that nothing is allocated while a CUDA graph is being captured
@@ -104,6 +148,10 @@ class DecodeStack:
         self._graph = None
 
     def step(self):
+        if self.glue:
+            for op in self.ops:
+                op()
+            return
         for lin, x, out in self.calls:
             lin(x, out=out, workspace_buf=self.workspace)
 
