@@ -44,13 +44,18 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(const XT* __restrict__ x
   const int lane = threadIdx.x & 31;
   const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int m0 = blockIdx.y * MT;
-  // Programmatic dependent launch: this grid may be scheduled while the previous kernel of the
-  // stream drains; x (possibly that kernel's output) and out are touched only after the wait.
-  griddep_launch_dependents();
-  griddep_wait();
-  if (n >= N) return;
+  // Programmatic dependent launch.  Weights and scales are constants, so a lane fetches its first
+  // chunk of them BEFORE waiting for the kernel ahead of it on the stream: that DRAM round trip then
+  // runs under the other kernel's tail.  x (possibly that kernel's output) and out are touched only
+  // after the wait.  A grid that fits on the machine at once lets the next kernel in right away
+  // (its launch and its own weight prefetch then overlap this kernel entirely); a larger grid does so
+  // only once its loads are issued, so that resident-but-waiting CTAs of the next kernel do not take
+  // SM slots from this grid's later waves.
+  const bool small_grid = gridDim.x * gridDim.y <= 296u;
+  if (small_grid) griddep_launch_dependents();
+  const bool row_ok = n < N;
   const int ns = K / G;
-  const ST* srow = scales + static_cast<long long>(n) * ns;
+  const ST* srow = scales + static_cast<long long>(row_ok ? n : 0) * ns;
   float acc[MT];
 #pragma unroll
   for (int m = 0; m < MT; ++m) acc[m] = 0.0f;
@@ -58,21 +63,37 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(const XT* __restrict__ x
   if (VEC) {
     // K % 8 == 0, G % 8 == 0, all rows 16-byte (x) / 4- or 8-byte (w) aligned.
     const int nchunks = K >> 3;
-#pragma unroll 4
-    for (int c = lane; c < nchunks; c += 32) {
+    const uint8_t* wrow8 = w + static_cast<long long>(row_ok ? n : 0) * (WBITS == 4 ? (K >> 1) : K);
+    constexpr int PRE = 4;       // chunks per lane fetched ahead of the wait (K <= 1024 is covered whole)
+    uint32_t pre_w0[PRE], pre_w1[PRE];
+    float pre_sc[PRE];
+#pragma unroll
+    for (int j = 0; j < PRE; ++j) {
+      const int c = lane + 32 * j;
+      pre_w0[j] = 0u; pre_w1[j] = 0u; pre_sc[j] = 0.0f;
+      if (row_ok && c < nchunks) {
+        if (WBITS == 4) {
+          pre_w0[j] = __ldg(reinterpret_cast<const uint32_t*>(wrow8) + c);
+        } else {
+          const uint2 two = __ldg(reinterpret_cast<const uint2*>(wrow8) + c);
+          pre_w0[j] = two.x; pre_w1[j] = two.y;
+        }
+        pre_sc[j] = to_f32<ST>(__ldg(srow + (c << 3) / G));
+      }
+    }
+    griddep_wait();
+    if (!row_ok) { if (!small_grid) griddep_launch_dependents(); return; }
+    auto chunk = [&](int c, uint32_t w0, uint32_t w1, float sc) {
       const int k0 = c << 3;
       float wq[8];
       if (WBITS == 4) {
-        const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(w + static_cast<long long>(n) * (K >> 1)) + c);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) wq[i] = small_uint_to_f32((word >> (4 * i)) & 15u) - 8.0f;
+        for (int i = 0; i < 8; ++i) wq[i] = small_uint_to_f32((w0 >> (4 * i)) & 15u) - 8.0f;
       } else {
-        const uint2 two = __ldg(reinterpret_cast<const uint2*>(w + static_cast<long long>(n) * K) + c);
         float f[4];
-        int8x4_to_f32(two.x, f); wq[0] = f[0]; wq[1] = f[1]; wq[2] = f[2]; wq[3] = f[3];
-        int8x4_to_f32(two.y, f); wq[4] = f[0]; wq[5] = f[1]; wq[6] = f[2]; wq[7] = f[3];
+        int8x4_to_f32(w0, f); wq[0] = f[0]; wq[1] = f[1]; wq[2] = f[2]; wq[3] = f[3];
+        int8x4_to_f32(w1, f); wq[4] = f[0]; wq[5] = f[1]; wq[6] = f[2]; wq[7] = f[3];
       }
-      const float sc = to_f32<ST>(__ldg(srow + k0 / G));
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
         if (m0 + m < M) {
@@ -84,8 +105,28 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(const XT* __restrict__ x
           acc[m] = fmaf(sc, p, acc[m]);
         }
       }
+    };
+#pragma unroll
+    for (int j = 0; j < PRE; ++j) {
+      const int c = lane + 32 * j;
+      if (c < nchunks) chunk(c, pre_w0[j], pre_w1[j], pre_sc[j]);
     }
+#pragma unroll 4
+    for (int c = lane + 32 * PRE; c < nchunks; c += 32) {
+      uint32_t w0, w1 = 0u;
+      if (WBITS == 4) {
+        w0 = __ldg(reinterpret_cast<const uint32_t*>(wrow8) + c);
+      } else {
+        const uint2 two = __ldg(reinterpret_cast<const uint2*>(wrow8) + c);
+        w0 = two.x; w1 = two.y;
+      }
+      chunk(c, w0, w1, to_f32<ST>(__ldg(srow + (c << 3) / G)));
+    }
+    if (!small_grid) griddep_launch_dependents();
   } else {
+    griddep_wait();
+    if (!small_grid) griddep_launch_dependents();
+    if (!row_ok) return;
     if (WBITS == 4) {
       const uint8_t* wrow = w + static_cast<long long>(n) * (K >> 1);
       for (int j = lane; j < (K >> 1); j += 32) {

@@ -7,11 +7,11 @@
 // with float32 arithmetic end to end, so it serves the reference's own dtypes (float32 x,
 // scales and out at 1e-4 relative) as well as 16-bit activations.
 //
-// Work decomposition.  A CTA owns 32 output rows and walks all of K in tiles of 32 rows x 256
-// bytes (one TMA box, 8 KB; K need only be a multiple of 16: the last box is filled with
-// zeros).  A producer warp keeps a 4-stage ring full; it starts before the kernel ahead of it
+// Work decomposition.  A CTA owns 16 output rows and walks all of K in tiles of 16 rows x 256
+// bytes (one TMA box, 4 KB; K need only be a multiple of 16: the last box is filled with
+// zeros).  A producer warp keeps an 8-stage ring full; it starts before the kernel ahead of it
 // on the stream has finished (weights are constants), while the four consumer warps wait for
-// that kernel before touching x.  Consumer warp w takes rows 8w .. 8w+7: a 256-byte tile row is
+// that kernel before touching x.  Consumer warp w takes rows 4w .. 4w+3: a 256-byte tile row is
 // 16 lanes x 16 bytes, so one 128-bit shared load serves two rows per warp instruction and a
 // lane holds 16 consecutive weights of one group (group_size % 16 == 0).  Per-lane partial sums
 // are combined with a 16-lane shuffle tree once, after the last tile.  No scratch memory, no
@@ -26,11 +26,12 @@
 namespace lcq {
 namespace gemv_w8 {
 
-constexpr int RB = 32;                       // rows per CTA and tile
+constexpr int RB = 16;                       // rows per CTA and tile
 constexpr int KB = 256;                      // weight bytes (= k) per tile row
-constexpr int STAGE_BYTES = RB * KB;         // 8192
-constexpr int NSTAGES = 4;
-constexpr int NCW = 4;                       // consumer warps, 8 rows each
+constexpr int STAGE_BYTES = RB * KB;         // 4096
+constexpr int NSTAGES = 8;
+constexpr int NCW = 4;                       // consumer warps, 4 rows each
+constexpr int RPW = RB / NCW / 2;            // 128-bit loads (two rows each) per warp and tile
 constexpr int NTHREADS = (NCW + 1) * 32;
 
 __device__ __forceinline__ uint4 lds128_w8(uint32_t a) {
@@ -101,33 +102,56 @@ __global__ void __launch_bounds__(NTHREADS) w8_gemv_kernel(const __grid_constant
     // ------------------------------------------------------------ consumers
     const int half = lane >> 4, seg = lane & 15;       // which of the two rows of a load; 16-byte segment of the tile row
     const int ns = K / G;
-    float acc[4][MM];
+    float acc[RPW][MM];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < RPW; ++i) {
 #pragma unroll
       for (int m = 0; m < MM; ++m) acc[i][m] = 0.0f;
     }
-    const uint32_t lane_addr = smem_u32(stages) + static_cast<uint32_t>((warp * 8 + half) * KB + seg * 16);
+    const uint32_t lane_addr = smem_u32(stages) + static_cast<uint32_t>((warp * (2 * RPW) + half) * KB + seg * 16);
     griddep_wait();                  // x may be the output of the kernel ahead of us; out may still be in its use
     bool dead = false;
+    // x and the scales of a tile come from global memory (L1 / L2): those of tile it+1 are fetched
+    // before the math of tile it, so their latency hides behind it.
+    float xn[MM <= 2 ? MM : 1][16];
+    float scn[RPW];
+    auto fetch = [&](int it) {
+      const int k0 = it * KB + seg * 16;
+      if (it < n_tiles && k0 < K) {
+        if (MM <= 2) {
+#pragma unroll
+          for (int m = 0; m < MM; ++m) {
+            if (m < M) load16<XT>(x + static_cast<long long>(m) * K + k0, xn[m]);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < RPW; ++i) {
+          const int row = row0 + warp * (2 * RPW) + 2 * i + half;
+          scn[i] = row < N ? load_scale(scales, s_dtype, static_cast<long long>(row) * ns + k0 / G) : 0.0f;
+        }
+      }
+    };
+    fetch(0);
     for (int it = 0; it < n_tiles; ++it) {
       const int s = it % NSTAGES;
       const uint32_t ph = (it / NSTAGES) & 1;
+      float xr[MM <= 2 ? MM : 1][16];
+      float sc[RPW];
+#pragma unroll
+      for (int m = 0; m < (MM <= 2 ? MM : 1); ++m) {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) xr[m][e] = xn[m][e];
+      }
+#pragma unroll
+      for (int i = 0; i < RPW; ++i) sc[i] = scn[i];
+      fetch(it + 1);
       if (!dead && (*reinterpret_cast<volatile int*>(&flag_abort) || !mbar_wait_bounded(&full_bar[s], ph))) {
         dead = true; flag_abort = 1; atomicExch(&g_device_status, 6);
       }
       const int k0 = it * KB + seg * 16;               // this lane's 16 consecutive k
       if (!dead && k0 < K) {
-        float xr[MM <= 2 ? MM : 1][16];
-        if (MM <= 2) {
 #pragma unroll
-          for (int m = 0; m < MM; ++m) {
-            if (m < M) load16<XT>(x + static_cast<long long>(m) * K + k0, xr[m]);
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int row = row0 + warp * 8 + 2 * i + half;
+        for (int i = 0; i < RPW; ++i) {
           const uint4 wv = lds128_w8(lane_addr + static_cast<uint32_t>(s * STAGE_BYTES + 2 * i * KB));
           float wf[16];
           {
@@ -137,7 +161,6 @@ __global__ void __launch_bounds__(NTHREADS) w8_gemv_kernel(const __grid_constant
             int8x4_to_f32(wv.z, f); wf[8] = f[0]; wf[9] = f[1]; wf[10] = f[2]; wf[11] = f[3];
             int8x4_to_f32(wv.w, f); wf[12] = f[0]; wf[13] = f[1]; wf[14] = f[2]; wf[15] = f[3];
           }
-          const float sc = row < N ? load_scale(scales, s_dtype, static_cast<long long>(row) * ns + k0 / G) : 0.0f;
 #pragma unroll
           for (int m = 0; m < MM; ++m) {
             if (m < M) {
@@ -151,7 +174,7 @@ __global__ void __launch_bounds__(NTHREADS) w8_gemv_kernel(const __grid_constant
 #pragma unroll
                 for (int e = 0; e < 16; ++e) dot = fmaf(xv[e], wf[e], dot);
               }
-              acc[i][m] = fmaf(sc, dot, acc[i][m]);
+              acc[i][m] = fmaf(sc[i], dot, acc[i][m]);
             }
           }
         }
@@ -161,13 +184,13 @@ __global__ void __launch_bounds__(NTHREADS) w8_gemv_kernel(const __grid_constant
     }
     // 16-lane tree: lanes 0-15 hold row (2i), lanes 16-31 row (2i+1) of the warp's 8 rows
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < RPW; ++i) {
 #pragma unroll
       for (int m = 0; m < MM; ++m) {
         float v = acc[i][m];
 #pragma unroll
         for (int off = 8; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-        const int row = row0 + warp * 8 + 2 * i + half;
+        const int row = row0 + warp * (2 * RPW) + 2 * i + half;
         if (seg == 0 && m < M && row < N) store_result(out, o_dtype, static_cast<long long>(m) * N + row, v);
       }
     }

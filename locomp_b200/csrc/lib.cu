@@ -199,8 +199,14 @@ static int select_algo(int wbits, int M, int N, int K, int G, int x_dtype, int s
   const bool long_k_few_rows = K > 16384 && M <= 64;
   if (wbits == 4 && M > 16 && !long_k_few_rows && gemm_tc::supported(M, N, K, G, x_dtype, scale_dtype))
     return LCQ_ALGO_GEMM_TC;
-  if (wbits == 4 && gemv_tc::supported(M < 16 ? M : 16, N, K, G, x_dtype, scale_dtype)) return LCQ_ALGO_GEMV_TC;
-  if (wbits == 8 && gemv_w8::supported(M, N, K, G)) return LCQ_ALGO_GEMV_W8;
+  // A single activation row against a weight of at most 2 Mi weights (1 MiB packed) is pure latency:
+  // the warp-per-row kernel has no ring to fill and no activations to stage, and measures
+  // ~2 us per call in a chain of dependent launches against ~4 us for the TMA-staged kernel.
+  const bool tiny_matvec = M == 1 && static_cast<long long>(N) * K <= (1LL << 21);
+  if (wbits == 4 && !tiny_matvec && gemv_tc::supported(M < 16 ? M : 16, N, K, G, x_dtype, scale_dtype)) return LCQ_ALGO_GEMV_TC;
+  // int8: the TMA-staged kernel has one CTA per 16 rows and no split along K; it pays off once that is
+  // several CTAs per SM, below that the warp-per-row kernel (8 rows per CTA) is faster
+  if (wbits == 8 && N >= 16384 && gemv_w8::supported(M, N, K, G)) return LCQ_ALGO_GEMV_W8;
   return LCQ_ALGO_SIMT;
 }
 

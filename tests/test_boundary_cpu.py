@@ -67,10 +67,13 @@ def test_algo_selection():
     sel = lib.lcq_matmul_select_algo
     assert sel(4, 1, 2048, 2048, 32, _lib.F16, _lib.F16, _lib.F16) == _lib.ALGO_GEMV_TC
     assert sel(4, 16, 2048, 8192, 32, _lib.F16, _lib.F16, _lib.F16) == _lib.ALGO_GEMV_TC
-    assert sel(4, 1, 1536, 576, 32, _lib.F16, _lib.F16, _lib.F16) == _lib.ALGO_GEMV_TC   # K % 256 != 0: partial last k tile
+    assert sel(4, 4, 1536, 576, 32, _lib.F16, _lib.F16, _lib.F16) == _lib.ALGO_GEMV_TC   # K % 256 != 0: partial last k tile
+    assert sel(4, 1, 49152, 576, 32, _lib.F16, _lib.F16, _lib.F16) == _lib.ALGO_GEMV_TC  # the lm_head
+    assert sel(4, 1, 1536, 576, 32, _lib.F16, _lib.F16, _lib.F16) == _lib.ALGO_SIMT      # one row x a tiny weight: latency-bound
     assert sel(4, 1, 1536, 96, 32, _lib.F16, _lib.F16, _lib.F16) == _lib.ALGO_SIMT       # K % 64 != 0
     assert sel(4, 1, 4096, 4096, 32, _lib.F32, _lib.F32, _lib.F32) == _lib.ALGO_SIMT     # reference dtypes
-    assert sel(8, 1, 1536, 576, 576, _lib.F32, _lib.F32, _lib.F32) == _lib.ALGO_GEMV_W8  # the reference's int8 shape
+    assert sel(8, 1, 1536, 576, 576, _lib.F32, _lib.F32, _lib.F32) == _lib.ALGO_SIMT     # the reference's int8 shape: 0.9 MB, latency-bound
+    assert sel(8, 1, 49152, 2048, 64, _lib.F32, _lib.F32, _lib.F32) == _lib.ALGO_GEMV_W8
     assert sel(8, 1, 64, 40, 8, _lib.F32, _lib.F32, _lib.F32) == _lib.ALGO_SIMT          # K % 16 != 0
     assert lib.lcq_matmul_workspace_bytes(8, 1, 1536, 576, 576, 0, 0, 0, 0) == 0
     assert lib.lcq_matmul_workspace_bytes(4, 1, 2048, 2048, 32, 1, 1, 1, 0) > 0

@@ -355,21 +355,20 @@ def test_w4a16_gemm_tc_unaligned_n_and_caller_workspace():
                                      (31, 16, 16, 2), (4096, 2048, 64, 5)])
 @pytest.mark.parametrize("xdt", ["f32", "f16"])
 def test_int8_tma_kernel_matches_oracle_and_simt(n, k, g, m, xdt):
-    """The TMA-staged int8 kernel (AUTO's choice for K % 16 == 0, G % 16 == 0, M <= 8) against the
+    """The TMA-staged int8 kernel (K % 16 == 0, G % 16 == 0, M <= 8; AUTO picks it from N = 16384 up) against the
     oracle, and against the CUDA-core kernel on the same inputs; partial last k tile, N tails."""
     rng = np.random.default_rng(n * 7 + k + m)
     w8, s8 = O.make_w8(rng, n, k, g, np.float32)
     x = rng.standard_normal((m, k)).astype(np.float32 if xdt == "f32" else np.float16)
     code = _lib.F32 if xdt == "f32" else _lib.F16
-    assert _lib.lib().lcq_matmul_select_algo(8, m, n, k, g, code, _lib.F32, code) == _lib.ALGO_GEMV_W8
     xd, wd, sd = torch.from_numpy(x).cuda(), torch.from_numpy(w8).cuda(), torch.from_numpy(s8).cuda()
-    y = L.quantized_matmul(xd, wd, sd, g, bits=8, out_dtype="f32")
+    y = L.quantized_matmul(xd, wd, sd, g, bits=8, out_dtype="f32", algo="gemv_w8")
     ref = O.matmul_int8(x.astype(np.float32), w8, s8, g)
     _assert_f32_close(y.cpu().numpy(), ref)
     y_simt = L.quantized_matmul(xd, wd, sd, g, bits=8, out_dtype="f32", algo="simt")
     _assert_f32_close(y.cpu().numpy(), y_simt.cpu().numpy())
     if xdt == "f16":
-        y16 = L.quantized_matmul(xd, wd, torch.from_numpy(s8.astype(np.float16)).cuda(), g, bits=8)
+        y16 = L.quantized_matmul(xd, wd, torch.from_numpy(s8.astype(np.float16)).cuda(), g, bits=8, algo="gemv_w8")
         assert y16.dtype == torch.float16
         _check16(y16.float().cpu().numpy(), O.matmul_int8(x.astype(np.float32), w8, s8.astype(np.float16), g))
     _device_status_ok()
