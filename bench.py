@@ -541,7 +541,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--gather", default="nccl", choices=["nccl", "nvlink"],
+    ap.add_argument("--gather", default="nvlink", choices=["nccl", "nvlink"],
                     help="multi-GPU: reassemble outputs with NCCL or with the library's peer-store kernel")
     ap.add_argument("--watchdog", type=int, default=900, help="abort the process after this many seconds")
     ap.add_argument("--profile-shape", default=None, metavar="KxNxM",

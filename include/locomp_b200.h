@@ -200,15 +200,17 @@ int lcq_quantize_int8(const void* w, void* w_int8, void* scales, int64_t N, int6
  * counterpart in the reference, which has no multi-GPU code.
  *
  * Each rank owns one region of lcq_peer_region_bytes(bytes_per_rank, world) bytes:
- * [256 bytes of flags][world slices].  lcq_peer_alloc allocates it (cudaMalloc, zero-filled -- a
- * set-up call, not for the hot path) and returns a 64-byte CUDA IPC handle to hand to the other
- * ranks; lcq_peer_open maps a peer's region from its handle.  lcq_allgather_push(src, ...,
- * regions[0..world-1], rank, world, state, stream) enqueues ONE kernel that stores this rank's
- * slice into slot `rank` of every region (peer stores only, never peer loads), publishes a
- * sequence number and waits -- bounded; on expiry lcq_check_device_status reports it -- until this
- * rank's own region holds every rank's slice of the same call.  `state`: 2 zero-initialised ints of
- * local device memory per region.  All ranks must issue the same sequence of pushes per region.
- * world <= 8; slices are multiples of 16 bytes.
+ * [256 bytes][data: world slices][staging: 2 x world x 2 slices].  lcq_peer_alloc allocates it
+ * (cudaMalloc, zero-filled -- a set-up call, not for the hot path) and returns a 64-byte CUDA IPC
+ * handle to hand to the other ranks; lcq_peer_open maps a peer's region from its handle.
+ * lcq_allgather_push(src, ..., regions[0..world-1], rank, world, state, stream) enqueues ONE kernel
+ * that stores this rank's slice, as {word, sequence number} pairs, into the staging area of every
+ * peer's region (peer stores only, never peer loads; no fence, no flag: the receiver polls the pairs
+ * themselves) and unpacks the peers' slices into the data area of its own region, which then holds
+ * every rank's slice of the call at byte offset 256 + r * bytes_per_rank.  The wait is bounded; on
+ * expiry lcq_check_device_status reports it.  `state`: 2 zero-initialised ints of local device memory
+ * per region.  All ranks must issue the same sequence of pushes per region.  world <= 8; slices are
+ * multiples of 16 bytes.
  */
 int lcq_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64);
 int lcq_peer_open(const unsigned char* handle64, void** ptr);

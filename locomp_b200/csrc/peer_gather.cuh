@@ -1,26 +1,16 @@
 // All-gather over NVLink peer memory for the N-column sharded linears: one kernel per rank
-// PUSHES its output slice into every rank's gathered buffer with plain peer stores, then signals
-// and waits on flags.  No loads from peer memory, no multicast, no NCCL on this path.
+// PUSHES its output slice into every rank's region with plain peer stores and unpacks what the
+// peers pushed.  No loads from peer memory, no multicast, no NCCL on this path.
 //
-// Every rank owns one region  [ flags: 64 ints | data: world x bytes_per_rank ]  allocated with
-// cudaMalloc and exported with a CUDA IPC handle; peers map it (cudaIpcOpenMemHandle).  A call
-//   1. copies this rank's slice into slot `rank` of every region (its own included),
-//   2. after the last CTA's stores are fenced system-wide, writes the call's sequence number
-//      into flags[rank] of every region,
-//   3. waits -- bounded by the library's wait limit -- until its own region shows that sequence number from every
-//      rank, so kernels that follow on the stream see the complete gathered buffer.
-// The sequence number lives in device memory and is advanced by the kernel itself, so a CUDA
-// graph that captured the launch can be replayed.  Ranks run on different GPUs (one process per
-// GPU); the wait is on other GPUs' kernels, never on another launch of the same GPU.
+// Every rank owns one region allocated with cudaMalloc and exported with a CUDA IPC handle; peers
+// map it (cudaIpcOpenMemHandle).  The sequence number of a region lives in device memory and is
+// advanced by the kernel itself, so a CUDA graph that captured the launch can be replayed.  Ranks
+// run on different GPUs (one process per GPU); the wait is on other GPUs' kernels, never on
+// another launch of the same GPU, and it is bounded by the library's wait limit.
 //
-// Reuse rule: a rank's push overwrites slot `rank` of EVERY rank's region as soon as it runs, so
-// a region may be pushed to again only when no rank can still be reading its previous contents.
-// A rank leaves push k only after it has seen every rank's flag of push k, i.e. every rank has
-// at least started push k; it has not necessarily finished reading the data of push k-1 on the
-// same region.  So between two pushes to one region there must be (a) the readers of the first,
-// enqueued ahead of the second push on every rank's stream, and (b) one complete push/wait round
-// on a DIFFERENT region, which proves that every rank's stream has passed those readers.  A
-// layer called back to back therefore alternates between two regions.
+// Reuse rule: the data area a push fills is read by the kernels that follow it on the stream; the
+// next push to the same region overwrites it, so those readers must be enqueued ahead of that push
+// (stream order does the rest).  A peer can run one call ahead of this rank, never two.
 #pragma once
 #include "common.cuh"
 
@@ -31,20 +21,27 @@ constexpr int MAX_RANKS = 8;
 constexpr int FLAG_BYTES = 256;
 
 struct PushArgs {
-  uint4* data[MAX_RANKS];        // data area of every rank's region (peer-mapped, own included)
-  int* flags[MAX_RANKS];         // flag area of every rank's region
+  uint4* data[MAX_RANKS];        // data area (followed by the staging area) of every rank's region, peer-mapped
   const uint4* src;
   long long n16;                 // 16-byte pieces per rank slice
   int rank, world;
   int* state;                    // local: [0] sequence number, [1] CTA arrival counter
 };
 
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// Low-latency form: every 4-byte word travels as an 8-byte {word, sequence number} pair, so the
+// receiver needs no flag, no fence and no barrier -- it polls the pair itself until the number of
+// the current call appears (8-byte stores arrive whole).  Each rank stores its slice, in that
+// form, into the staging area of every peer's region (peer stores only), then unpacks what the
+// peers stored into its own region's data area.  Two staging buffers alternate by call parity: a
+// peer can start call n+1 while this rank still reads call n, but cannot start call n+2 before
+// this rank has started n+1 (it needs this rank's slice of n+1 to finish), so two are enough.
+// Region layout:  [ 256 B unused | data: world x slice | staging: 2 x world x 2*slice ].
+__device__ __forceinline__ void st_volatile_v4(uint4* p, uint4 v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-  int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
 
@@ -54,40 +51,62 @@ __global__ void __launch_bounds__(256) allgather_push_kernel(const PushArgs a) {
   // touches activations, outputs and scratch only after this grid has completed).
   griddep_launch_dependents();
   griddep_wait();                // src is the output of the kernel before us on the stream
+  const uint32_t seq = static_cast<uint32_t>(*reinterpret_cast<volatile int*>(&a.state[0])) + 1u;
+  const long long buf = static_cast<long long>(seq & 1u) * a.world;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < a.n16; i += stride) {
+  const long long first = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  // send
+  for (long long i = first; i < a.n16; i += stride) {
     const uint4 v = a.src[i];
-    const long long o = static_cast<long long>(a.rank) * a.n16 + i;
+    const uint4 lo = make_uint4(v.x, seq, v.y, seq), hi = make_uint4(v.z, seq, v.w, seq);
 #pragma unroll
-    for (int g = 0; g < MAX_RANKS; ++g)
-      if (g < a.world) a.data[g][o] = v;
+    for (int g = 0; g < MAX_RANKS; ++g) {
+      if (g < a.world && g != a.rank) {
+        uint4* dst = a.data[g] + static_cast<long long>(a.world) * a.n16 + ((buf + a.rank) * a.n16 + i) * 2;
+        st_volatile_v4(dst, lo);
+        st_volatile_v4(dst + 1, hi);
+      }
+    }
+    a.data[a.rank][static_cast<long long>(a.rank) * a.n16 + i] = v;
   }
-  __syncthreads();
-  if (threadIdx.x != 0) return;
-  __threadfence_system();        // one fence per CTA, after the barrier: covers every thread's slice stores
-  if (gridDim.x > 1) {
-    const int prev = atomicAdd(&a.state[1], 1);
-    if (prev != static_cast<int>(gridDim.x) - 1) return;
-    a.state[1] = 0;
-    __threadfence_system();      // last CTA: the other CTAs' fenced stores are ordered before the flags below
-  }
-  // every slice store of this rank is visible system-wide: publish, then wait for the peers
-  const int seq = a.state[0] + 1;
-  a.state[0] = seq;
-  for (int g = 0; g < a.world; ++g) st_release_sys(a.flags[g] + a.rank, seq);
+  // receive: bounded polling on this rank's own staging area
   const uint64_t t0 = global_timer_ns();
   const uint64_t limit = wait_limit_ns();
-  const int* mine = a.flags[a.rank];
-  for (int r = 0; r < a.world; ++r) {
-    while (ld_acquire_sys(mine + r) - seq < 0) {                     // wrap-safe "not yet"
-      if (global_timer_ns() - t0 > limit) { atomicExch(&g_device_status, 30 + r); return; }
+  bool gave_up = false;
+  for (int r = 0; r < a.world && !gave_up; ++r) {
+    if (r == a.rank) continue;
+    const uint4* stage = a.data[a.rank] + static_cast<long long>(a.world) * a.n16 + (buf + r) * a.n16 * 2;
+    for (long long i = first; i < a.n16 && !gave_up; i += stride) {
+      uint4 lo, hi;
+      int spins = 0;
+      for (;;) {
+        lo = ld_volatile_v4(stage + 2 * i);
+        hi = ld_volatile_v4(stage + 2 * i + 1);
+        if (lo.y == seq && lo.w == seq && hi.y == seq && hi.w == seq) break;
+        if ((++spins & 63) == 0 && global_timer_ns() - t0 > limit) {
+          atomicExch(&g_device_status, 30 + r);
+          gave_up = true;
+          break;
+        }
+      }
+      if (!gave_up) a.data[a.rank][static_cast<long long>(r) * a.n16 + i] = make_uint4(lo.x, lo.z, hi.x, hi.z);
+    }
+  }
+  // the last CTA to finish advances the sequence number (every CTA has read it by then)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(&a.state[1], 1);
+    if (prev == static_cast<int>(gridDim.x) - 1) {
+      a.state[1] = 0;
+      a.state[0] = static_cast<int>(seq);
+      __threadfence();
     }
   }
 }
 
 inline int launch_push(const PushArgs& a, cudaStream_t stream) {
   long long blocks = (a.n16 + 255) / 256;
-  if (blocks > 32) blocks = 32;
+  if (blocks > 64) blocks = 64;
   if (blocks < 1) blocks = 1;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));

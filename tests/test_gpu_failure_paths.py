@@ -28,8 +28,10 @@ def test_bounded_wait_runs_out_and_the_context_survives():
         assert lib.lcq_allgather_push(src.data_ptr(), nbytes, regions, 0, 2, state.data_ptr(), None) == 0
         assert lib.lcq_check_device_status(None) == _lib.ERR_TIMEOUT
         assert b"bounded wait" in lib.lcq_last_error()
-        # this rank's slice did arrive in slot 0 of both regions before the wait gave up
-        assert torch.equal(mine[256:256 + nbytes], src) and torch.equal(absent_peer[256:256 + nbytes], src)
+        # this rank's slice is in slot 0 of its own region, and was pushed (as {word, sequence} pairs)
+        # into the peer's staging area, before the wait gave up
+        assert torch.equal(mine[256:256 + nbytes], src)
+        assert int(absent_peer[256 + 2 * nbytes:].count_nonzero()) > 0 and int(absent_peer[256:256 + 2 * nbytes].count_nonzero()) == 0
         # the status word was cleared by the read, and the next kernel runs normally
         assert lib.lcq_check_device_status(None) == 0
         rng = np.random.default_rng(1)
