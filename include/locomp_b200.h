@@ -207,7 +207,10 @@ int lcq_quantize_int8(const void* w, void* w_int8, void* scales, int64_t N, int6
  * that stores this rank's slice, as {word, sequence number} pairs, into the staging area of every
  * peer's region (peer stores only, never peer loads; no fence, no flag: the receiver polls the pairs
  * themselves) and unpacks the peers' slices into the data area of its own region, which then holds
- * every rank's slice of the call at byte offset 256 + r * bytes_per_rank.  The wait is bounded; on
+ * every rank's slice of the call at byte offset 256 + r * bytes_per_rank.  (Slices so large that the
+ * pairs would add more than 1 MiB per call are instead stored plainly into the peers' data areas,
+ * followed by a system-wide fence and per-rank sequence flags; with such slices, alternate between
+ * two regions, because peers then write into the area the previous call's readers use.)  The wait is bounded; on
  * expiry lcq_check_device_status reports it.  `state`: 2 zero-initialised ints of local device memory
  * per region.  All ranks must issue the same sequence of pushes per region.  world <= 8; slices are
  * multiples of 16 bytes.

@@ -534,6 +534,7 @@ int lcq_allgather_push(const void* src, size_t bytes_per_rank, void* const* regi
   memset(&a, 0, sizeof(a));
   for (int g = 0; g < world; ++g) {
     if (!regions[g]) { set_error("lcq_allgather_push: region %d is null", g); return LCQ_ERR_BAD_ARG; }
+    a.flags[g] = static_cast<int*>(regions[g]);
     a.data[g] = reinterpret_cast<uint4*>(static_cast<uint8_t*>(regions[g]) + peer::FLAG_BYTES);
   }
   a.src = static_cast<const uint4*>(src);

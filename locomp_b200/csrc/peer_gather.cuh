@@ -10,7 +10,9 @@
 //
 // Reuse rule: the data area a push fills is read by the kernels that follow it on the stream; the
 // next push to the same region overwrites it, so those readers must be enqueued ahead of that push
-// (stream order does the rest).  A peer can run one call ahead of this rank, never two.
+// (stream order does the rest).  A peer can run one call ahead of this rank, never two.  Large slices
+// take the bulk form below, whose stores land in the data area itself: there, callers alternate
+// between two regions.
 #pragma once
 #include "common.cuh"
 
@@ -22,6 +24,7 @@ constexpr int FLAG_BYTES = 256;
 
 struct PushArgs {
   uint4* data[MAX_RANKS];        // data area (followed by the staging area) of every rank's region, peer-mapped
+  int* flags[MAX_RANKS];         // first 256 bytes of every rank's region: one sequence flag per rank (bulk form)
   const uint4* src;
   long long n16;                 // 16-byte pieces per rank slice
   int rank, world;
@@ -35,7 +38,7 @@ struct PushArgs {
 // peers stored into its own region's data area.  Two staging buffers alternate by call parity: a
 // peer can start call n+1 while this rank still reads call n, but cannot start call n+2 before
 // this rank has started n+1 (it needs this rank's slice of n+1 to finish), so two are enough.
-// Region layout:  [ 256 B unused | data: world x slice | staging: 2 x world x 2*slice ].
+// Region layout:  [ 256 B of flags (bulk form) | data: world x slice | staging: 2 x world x 2*slice ].
 __device__ __forceinline__ void st_volatile_v4(uint4* p, uint4 v) {
   asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
@@ -104,9 +107,62 @@ __global__ void __launch_bounds__(256) allgather_push_kernel(const PushArgs a) {
   }
 }
 
+// Bulk form, for slices large enough that doubling the bytes costs more than two fences: plain
+// stores of the slice into slot `rank` of every region's data area, a system-wide fence after the
+// last CTA's stores, this rank's sequence number into flags[rank] of every region, then a bounded
+// wait until the own region shows the number from every rank.  Because peers write straight into
+// the data area, a region must not be pushed to again while any rank may still read its previous
+// contents: callers alternate between two regions.
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(256) allgather_bulk_kernel(const PushArgs a) {
+  griddep_launch_dependents();
+  griddep_wait();                // src is the output of the kernel before us on the stream
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < a.n16; i += stride) {
+    const uint4 v = a.src[i];
+    const long long o = static_cast<long long>(a.rank) * a.n16 + i;
+#pragma unroll
+    for (int g = 0; g < MAX_RANKS; ++g)
+      if (g < a.world) a.data[g][o] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  __threadfence_system();        // one fence per CTA, after the barrier: covers every thread's slice stores
+  if (gridDim.x > 1) {
+    const int prev = atomicAdd(&a.state[1], 1);
+    if (prev != static_cast<int>(gridDim.x) - 1) return;
+    a.state[1] = 0;
+    __threadfence_system();      // last CTA: the other CTAs' fenced stores are ordered before the flags below
+  }
+  const int seq = a.state[0] + 1;
+  a.state[0] = seq;
+  for (int g = 0; g < a.world; ++g) st_release_sys(a.flags[g] + a.rank, seq);
+  const uint64_t t0 = global_timer_ns();
+  const uint64_t limit = wait_limit_ns();
+  const int* mine = a.flags[a.rank];
+  for (int r = 0; r < a.world; ++r) {
+    while (ld_acquire_sys(mine + r) - seq < 0) {                     // wrap-safe "not yet"
+      if (global_timer_ns() - t0 > limit) { atomicExch(&g_device_status, 30 + r); return; }
+    }
+  }
+}
+
+// The pair form doubles the bytes on the wire and saves two fences (a few microseconds): it is used
+// while the extra bytes to all peers stay under 1 MiB.  Every rank takes the same decision.
+inline bool use_pairs(long long bytes_per_rank, int world) { return bytes_per_rank * (world - 1) <= (1LL << 20); }
+
 inline int launch_push(const PushArgs& a, cudaStream_t stream) {
+  const bool pairs = use_pairs(a.n16 * 16, a.world);
   long long blocks = (a.n16 + 255) / 256;
-  if (blocks > 64) blocks = 64;
+  if (blocks > (pairs ? 64 : 32)) blocks = pairs ? 64 : 32;
   if (blocks < 1) blocks = 1;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -118,7 +174,8 @@ inline int launch_push(const PushArgs& a, cudaStream_t stream) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
-  LCQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, allgather_push_kernel, a));
+  if (pairs) LCQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, allgather_push_kernel, a));
+  else LCQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, allgather_bulk_kernel, a));
   return LCQ_OK;
 }
 
