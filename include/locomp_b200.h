@@ -89,6 +89,14 @@ int lcq_dequant_int8(const void* w_int8, const void* scales, void* out,
  * ZERO-FILLED before its first use; the kernels leave it zeroed again, so one buffer can be
  * reused by consecutive calls on one stream.  Calls that may overlap on the GPU need separate
  * workspaces.  May be NULL when the size query returns 0.
+ *
+ * Preconditions.  (1) The kernels are launched with programmatic stream serialisation and fetch
+ * w_packed / scales BEFORE the kernel ahead of them on the stream has finished: both must be complete
+ * before that kernel starts (weights written on the same stream need one synchronisation before the
+ * first matmul), or set LCQ_NO_PDL=1 in the environment.  x, out and workspace are touched only after
+ * that kernel has completed.  (2) With F16/BF16 activations the tensor-core kernels compute in fp16:
+ * |x| must not exceed 65504, and |x| below about 1e-3 loses precision in the M <= 16 kernel (it divides
+ * half of the activations by 16, into fp16's subnormal range).  F32 activations take a float32 kernel.
  */
 int lcq_matmul_int4(const void* x, const void* w_packed, const void* scales, void* out,
                     int M, int N, int K, int group_size,
@@ -222,6 +230,32 @@ int lcq_peer_free(void* ptr);
 int lcq_allgather_push(const void* src, size_t bytes_per_rank, void* const* regions, int rank, int world,
                        void* state, void* stream);
 size_t lcq_peer_region_bytes(size_t bytes_per_rank, int world);
+
+/*
+ * Sharding context for a host that is not Python: one per rank (one process per GPU), for linears
+ * whose output columns are split across the GPUs of one box.  No counterpart in the reference.
+ *   lcq_shard_ctx_create   allocates this rank's two gather regions (for slices of up to
+ *                          max_slice_bytes = M * N/world * sizeof(out)), its scratch, and returns two
+ *                          64-byte IPC handles (128 bytes) to hand to the other ranks by any means.
+ *   lcq_shard_ctx_connect  maps the peers' regions: all_handles = world x 128 bytes, rank-major.
+ *                          Every rank must have created its context before any rank connects.
+ *   lcq_sharded_matmul_int4  runs lcq_matmul_int4 on this rank's row block (w_local [N_total/world, K/2],
+ *                          scales_local [N_total/world, K/G]) with the replicated x [M, K], then the
+ *                          peer all-gather, both on `stream`; *gathered = device pointer to
+ *                          [world, M, N_total/world] of out_dtype (row-major [1, N_total] when M = 1),
+ *                          valid until the call after next on this context (two regions alternate).
+ *                          The first call of a problem size allocates its workspace (cudaMalloc,
+ *                          synchronises the device); later calls allocate nothing.
+ *   lcq_shard_ctx_destroy  synchronises the device and frees everything; every rank, after its last call.
+ * Set-up and tear-down are not for the hot path.  All ranks must issue the same sequence of calls.
+ */
+typedef struct lcq_shard_ctx lcq_shard_ctx;
+int lcq_shard_ctx_create(int rank, int world, size_t max_slice_bytes, lcq_shard_ctx** ctx, unsigned char* handles128);
+int lcq_shard_ctx_connect(lcq_shard_ctx* ctx, const unsigned char* all_handles);
+int lcq_sharded_matmul_int4(lcq_shard_ctx* ctx, const void* x, const void* w_local, const void* scales_local,
+                            void** gathered, int M, int N_total, int K, int group_size,
+                            int x_dtype, int scale_dtype, int out_dtype, int algo, void* stream);
+int lcq_shard_ctx_destroy(lcq_shard_ctx* ctx);
 
 /*
  * Device-side status word.  Kernels that wait on an mbarrier do so with an iteration limit;

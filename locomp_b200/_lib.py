@@ -47,6 +47,10 @@ SIGNATURES = {
     "lcq_allgather_push": (_c.c_int, [_c.c_void_p, _c.c_size_t, _c.POINTER(_c.c_void_p), _c.c_int, _c.c_int,
                                       _c.c_void_p, _c.c_void_p]),
     "lcq_peer_region_bytes": (_c.c_size_t, [_c.c_size_t, _c.c_int]),
+    "lcq_shard_ctx_create": (_c.c_int, [_c.c_int, _c.c_int, _c.c_size_t, _c.POINTER(_c.c_void_p), _c.c_char_p]),
+    "lcq_shard_ctx_connect": (_c.c_int, [_c.c_void_p, _c.c_char_p]),
+    "lcq_sharded_matmul_int4": (_c.c_int, [_c.c_void_p] * 4 + [_c.POINTER(_c.c_void_p)] + [_c.c_int] * 8 + [_c.c_void_p]),
+    "lcq_shard_ctx_destroy": (_c.c_int, [_c.c_void_p]),
     "lcq_check_device_status": (_c.c_int, [_c.c_void_p]),
     "lcq_set_wait_limit_ns": (_c.c_int, [_c.c_ulonglong]),
     "lcq_gemv_tc_plan_check": (_c.c_int, [_c.c_int] * 4 + [_c.POINTER(_c.c_int)]),

@@ -68,6 +68,11 @@ static_assert(static_cast<size_t>(MAX_ROW_BLOCKS) * COUNTERS_PER_RB * sizeof(int
 template <int MT> struct Cfg;
 template <> struct Cfg<1> { static constexpr int NCW = 8, NSTAGES = 4, CTAS_PER_SM = 2; };
 template <> struct Cfg<2> { static constexpr int NCW = 16, NSTAGES = 6, CTAS_PER_SM = 1; };
+// Ring depth.  In cluster mode a CTA owns at most S / cluster tiles of one row block, so a short ring
+// holds (nearly) all of them and leaves room for the reduction buffer.
+__host__ __device__ constexpr int nstages_for(int MT, bool CL) { return MT == 1 ? (CL ? 3 : Cfg<1>::NSTAGES) : (CL ? 4 : Cfg<2>::NSTAGES); }
+// bytes one CTA hands to its cluster leader per row group: 2 slabs x MT x 4 values x 32 lanes x 4 B
+__host__ __device__ constexpr int red_slot_bytes(int MT) { return 2 * MT * 4 * 32 * 4; }
 __host__ __device__ constexpr int max_dynamic_smem(int ctas_per_sm) { return (227 * 1024) / ctas_per_sm - (ctas_per_sm > 1 ? 1024 : 0); }
 // bytes of the slice hand-over buffer: (PARTS - 1) writers x 4 row groups x 2 slabs x MT x 4 values x 32 lanes
 __host__ __device__ constexpr int comb_bytes(int MT) { return ((MT == 1 ? 8 : 16) / NRG - 1) * NRG * 2 * MT * 4 * 32 * 4; }
@@ -91,6 +96,8 @@ struct Params {
   int nst;              // ceil(K / 256)
   int ctas_per_kr;      // CTAs working on one k-range
   int max_split;        // scratch slots per (row block, k-range)
+  int x_tiles;          // k tiles of x a CTA keeps in shared memory (S, or ceil(S / cluster) in cluster mode)
+  int cluster;          // CTAs per row block that reduce through distributed shared memory (1 = none)
 };
 
 // The share of one k-range's tile sequence owned by one CTA.  Tile counts are 32-bit: the plan
@@ -131,20 +138,22 @@ __host__ __device__ inline int contributors(const Params& p, int rb) {
 
 struct SmemLayout {     // offsets from the 1024-byte aligned base
   int comb;     // slice hand-over buffer
-  int xs;       // staged activations: [group][MPAD][4] x 16 B (+ 64 spare bytes)
-  int zps;      // zero-point quads: [group][row pair] x {z(m0), z(m1), z(m0), z(m1)}, z = -8 * xsum * 2^-24 (+ 64 spare bytes)
-  int bars;     // full[NSTAGES], empty[NSTAGES]
+  int xs;       // staged activations: [visited tile][group][MPAD][4] x 16 B (+ 64 spare bytes)
+  int zps;      // zero-point quads: [visited tile][group][row pair] x {z(m0), z(m1), z(m0), z(m1)}, z = -8 * xsum * 2^-24 (+ 64 spare bytes)
+  int bars;     // full[NSTAGES], empty[NSTAGES], red[NRG]
   int flags;    // CtaInfo (abort flag first)
+  int red;      // cluster mode, read by the leader only: [rank - 1][row group] slots of red_slot_bytes(MT)
   int total;
 };
-__host__ __device__ inline SmemLayout smem_layout(int nstages, int MPAD, int MT, int S) {
+__host__ __device__ inline SmemLayout smem_layout(int nstages, int MPAD, int MT, int x_tiles, int cluster) {
   SmemLayout L;
   L.comb = nstages * STAGE_BYTES;
   L.xs = L.comb + comb_bytes(MT);
-  L.zps = L.xs + S * GT * MPAD * 64 + 64;
-  L.bars = L.zps + S * GT * zq_group_bytes(MPAD) + 64;
-  L.flags = L.bars + 2 * nstages * 8;
-  L.total = L.flags + 64;
+  L.zps = L.xs + x_tiles * GT * MPAD * 64 + 64;
+  L.bars = L.zps + x_tiles * GT * zq_group_bytes(MPAD) + 64;
+  L.flags = L.bars + (2 * nstages + NRG) * 8;
+  L.red = L.flags + 64;
+  L.total = L.red + (cluster > 1 ? (cluster - 1) * NRG * red_slot_bytes(MT) : 0);
   return L;
 }
 
@@ -217,6 +226,54 @@ __device__ __forceinline__ bool mbar_wait_bounded_a(uint32_t bar, uint32_t parit
   return mbar_wait_slow(bar, parity, abort_addr);
 }
 
+// ---- thread-block cluster helpers (cluster mode: the CTAs of a row block add their partial
+//      results in the leader's shared memory instead of going through global scratch)
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Hardware cluster barrier, used once: arrive at kernel entry, wait before the first remote access
+// (shared memory of another CTA may only be touched once that CTA has started).
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+// shared::cluster address of `local_addr` (a shared::cta address) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(rank));
+  return a;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+// Arrival on another CTA's mbarrier; the release makes this thread's earlier remote stores visible
+// to whoever acquires the barrier's phase.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_acq_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded like every other wait of the kernel: gives up at the library's wait limit.
+__device__ __noinline__ bool mbar_wait_cluster_bounded(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait_acq_cluster(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  const uint64_t limit = wait_limit_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (mbar_try_wait_acq_cluster(bar, parity)) return true;
+    }
+    if (global_timer_ns() - t0 > limit) return false;
+  }
+}
+
 // What one thread works out for the whole CTA before the first barrier (schedule arithmetic needs
 // several integer divisions; the other threads read the results from shared memory).
 struct CtaInfo {
@@ -232,6 +289,21 @@ struct CtaInfo {
   int pad;
 };
 static_assert(sizeof(CtaInfo) == 48, "CtaInfo layout");
+
+// Walks the scratch slots of a row block in slot order: k-range kk holds its contributors in slots
+// kk * max_split .. kk * max_split + cnt(kk) - 1.  next() returns -1 when all have been visited.
+struct SlotIter {
+  int n_kr, c_full, c_last, max_split, kk, c;
+  __device__ SlotIter(int n_kr_, int c_full_, int c_last_, int max_split_)
+      : n_kr(n_kr_), c_full(c_full_), c_last(c_last_), max_split(max_split_), kk(0), c(0) {}
+  __device__ __forceinline__ int next() {
+    if (kk >= n_kr) return -1;
+    const int os = kk * max_split + c;
+    const int cnt = (kk == n_kr - 1) ? c_last : c_full;
+    if (++c >= cnt) { c = 0; ++kk; }
+    return os;
+  }
+};
 
 // Settles the 32 rows of one row group at the end of a CTA's share of a row block (called by the
 // row group's slice-0 warp with the slices already added up in y).  `whole`: the CTA produced the
@@ -303,39 +375,42 @@ __device__ __noinline__ void flush_row_group(const Params& p, const float (&y)[2
       for (int jm = 0; jm < MT; ++jm)
 #pragma unroll
         for (int e = 0; e < NC; ++e) { sum[sl][jm][e][0] = 0.0f; sum[sl][jm][e][1] = 0.0f; }
-    for (int kk = 0; kk < p.n_kr; ++kk) {
-      const int cnt = (kk == p.n_kr - 1) ? c_last : c_full;
-      for (int c = 0; c < cnt; ++c) {
-        const int os = kk * p.max_split + c;
-        float v[2][MT][NC][2];
-        if (os == slot) {
+    // CU contributors per pass: all loads of a pass are independent and in flight together; the
+    // additions follow slot order (the reducer below uses the same order, so both paths give the same bits).
+    constexpr int CU = (MT == 1 && NC == 1) ? 8 : (MT == 1 ? 4 : 2);
+    SlotIter iter(p.n_kr, c_full, c_last, p.max_split);
+    for (int done = 0; done < n_contrib; done += CU) {
+      float v[CU][2][MT][NC][2];
+      bool mine[CU];
 #pragma unroll
-          for (int sl = 0; sl < 2; ++sl)
-#pragma unroll
-            for (int jm = 0; jm < MT; ++jm)
-#pragma unroll
-              for (int e = 0; e < NC; ++e) { v[sl][jm][e][0] = y[sl][jm][e]; v[sl][jm][e][1] = y[sl][jm][2 + e]; }
-        } else {
-          const float* src = rb_part + os * slot_elems + r0;
-#pragma unroll
-          for (int sl = 0; sl < 2; ++sl)
-#pragma unroll
-            for (int jm = 0; jm < MT; ++jm)
-#pragma unroll
-              for (int e = 0; e < NC; ++e) {
-                const int m = 8 * jm + 2 * t4 + e;
-                const bool ok = m < p.M;
-                v[sl][jm][e][0] = ok ? __ldcg(src + m * ROWS + 16 * sl) : 0.0f;
-                v[sl][jm][e][1] = ok ? __ldcg(src + m * ROWS + 16 * sl + 8) : 0.0f;
-              }
-        }
+      for (int u = 0; u < CU; ++u) {
+        const int os = iter.next();                      // -1 past the end
+        mine[u] = os == slot;
+        const float* src = rb_part + (os < 0 ? 0 : os) * slot_elems + r0;
+        const bool live = os >= 0 && !mine[u];
 #pragma unroll
         for (int sl = 0; sl < 2; ++sl)
 #pragma unroll
           for (int jm = 0; jm < MT; ++jm)
 #pragma unroll
-            for (int e = 0; e < NC; ++e) { sum[sl][jm][e][0] += v[sl][jm][e][0]; sum[sl][jm][e][1] += v[sl][jm][e][1]; }
+            for (int e = 0; e < NC; ++e) {
+              const int m = 8 * jm + 2 * t4 + e;
+              const bool ok = live && m < p.M;
+              v[u][sl][jm][e][0] = ok ? __ldcg(src + m * ROWS + 16 * sl) : 0.0f;
+              v[u][sl][jm][e][1] = ok ? __ldcg(src + m * ROWS + 16 * sl + 8) : 0.0f;
+            }
       }
+#pragma unroll
+      for (int u = 0; u < CU; ++u)
+#pragma unroll
+        for (int sl = 0; sl < 2; ++sl)
+#pragma unroll
+          for (int jm = 0; jm < MT; ++jm)
+#pragma unroll
+            for (int e = 0; e < NC; ++e) {
+              sum[sl][jm][e][0] += mine[u] ? y[sl][jm][e] : v[u][sl][jm][e][0];
+              sum[sl][jm][e][1] += mine[u] ? y[sl][jm][2 + e] : v[u][sl][jm][e][1];
+            }
     }
 #pragma unroll
     for (int sl = 0; sl < 2; ++sl) {
@@ -384,16 +459,21 @@ __device__ __noinline__ void flush_row_group(const Params& p, const float (&y)[2
     float sum[MR];
 #pragma unroll
     for (int m = 0; m < MR; ++m) sum[m] = 0.0f;
-    for (int kk = 0; kk < p.n_kr; ++kk) {
-      const int cnt = (kk == p.n_kr - 1) ? c_last : c_full;
-      for (int c = 0; c < cnt; ++c) {
-        const float* sp = src + (kk * p.max_split + c) * slot_elems;
-        float v[MR];
+    constexpr int CU = MT == 1 ? 4 : 2;      // contributors per pass, their loads in flight together
+    SlotIter iter(p.n_kr, c_full, c_last, p.max_split);
+    for (int done = 0; done < n_contrib; done += CU) {
+      float v[CU][MR];
 #pragma unroll
-        for (int m = 0; m < MR; ++m) v[m] = m < p.M ? __ldcg(sp + m * ROWS) : 0.0f;
+      for (int u = 0; u < CU; ++u) {
+        const int os = iter.next();
+        const float* sp = src + (os < 0 ? 0 : os) * slot_elems;
 #pragma unroll
-        for (int m = 0; m < MR; ++m) sum[m] += v[m];
+        for (int m = 0; m < MR; ++m) v[u][m] = (os >= 0 && m < p.M) ? __ldcg(sp + m * ROWS) : 0.0f;
       }
+#pragma unroll
+      for (int u = 0; u < CU; ++u)
+#pragma unroll
+        for (int m = 0; m < MR; ++m) sum[m] += v[u][m];
     }
     const int n = rb * ROWS + rg * 32 + lane;
     if (n < p.N) {
@@ -407,11 +487,17 @@ __device__ __noinline__ void flush_row_group(const Params& p, const float (&y)[2
 
 // MT: 8-wide m tiles (1 or 2).  MPAD: rows of x per group in shared memory (>= M; 1, 2, 4, 8 or 16),
 // a compile-time stride.  RAGGED: K % 256 != 0 (scales by cp.async, activations beyond K staged as zeros).
-template <int MT, int MPAD, bool RAGGED>
+//
+// CL: cluster mode, for problems too small to give every CTA several tiles.  A row block belongs
+// to a cluster of p.cluster CTAs; CTA r of the cluster streams the r-th share of the row block's k
+// tiles, then hands its 128 x M partial to the cluster's first CTA through distributed shared
+// memory (remote stores + one remote mbarrier arrival per lane), and that CTA adds the shares in
+// rank order and writes the output.  No global scratch, no counters, no atomics.
+template <int MT, int MPAD, bool RAGGED, bool CL>
 __global__ void __launch_bounds__((Cfg<MT>::NCW + 1) * 32, Cfg<MT>::CTAS_PER_SM)
 w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_s,
                   const __grid_constant__ Params p) {
-  constexpr int NSTAGES = Cfg<MT>::NSTAGES;
+  constexpr int NSTAGES = nstages_for(MT, CL);
   constexpr int NCW = Cfg<MT>::NCW;
   constexpr int PARTS = NCW / NRG;            // slices of a tile's 8 groups (2 or 4)
   constexpr int CPW = GT / PARTS;             // groups per warp and tile (4 or 2)
@@ -424,7 +510,7 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     if (threadIdx.x == 0) atomicExch(&g_device_status, 3);
     return;
   }
-  const SmemLayout L = smem_layout(NSTAGES, MPAD, MT, p.S);
+  const SmemLayout L = smem_layout(NSTAGES, MPAD, MT, p.x_tiles, CL ? p.cluster : 1);
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar_addr = sbase + static_cast<uint32_t>(L.bars);      // full[s] at +8*s, empty[s] at +8*(NSTAGES+s)
   const uint32_t abort_addr = sbase + static_cast<uint32_t>(L.flags);   // CtaInfo::abort
@@ -445,9 +531,15 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
       ci.n_tiles = static_cast<int>(tile_begin(sch, ci.j + 1) - ci.t0);
       ci.rb0 = static_cast<int>(ci.t0 / static_cast<unsigned>(sch.S_kr));
       ci.ks0 = static_cast<int>(ci.t0 - static_cast<unsigned>(ci.rb0) * sch.S_kr);
+    }
+    if (CL && ci.leave) ci.rb0 = ci.j / p.cluster;   // (never planned) it would hand zeros to its own leader
+    if (CL || !ci.leave) {   // a cluster CTA always runs to the hand-over, tiles or not
       for (int s = 0; s < NSTAGES; ++s) {
         mbar_init(reinterpret_cast<uint64_t*>(smem + L.bars) + s, RAGGED ? 33 : 1);
         mbar_init(reinterpret_cast<uint64_t*>(smem + L.bars) + NSTAGES + s, NCW);
+      }
+      if (CL) {   // one arrival per lane of each other CTA's row-group warp
+        for (int r = 0; r < NRG; ++r) mbar_init(reinterpret_cast<uint64_t*>(smem + L.bars) + 2 * NSTAGES + r, (p.cluster - 1) * 32);
       }
       fence_barrier_init();
     }
@@ -458,7 +550,8 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     griddep_launch_dependents();
   }
   __syncthreads();
-  if (info->leave) return;  // whole CTA leaves together; nothing was started
+  if (CL) cluster_arrive();   // "this CTA runs and its barriers exist"; no CTA leaves early in cluster mode
+  if (!CL && info->leave) return;  // whole CTA leaves together; nothing was started
   const unsigned t0 = info->t0;
   const int n_tiles = info->n_tiles;
   const int rb0 = info->rb0, ks0 = info->ks0, kr = info->kr, S_kr = info->S_kr;
@@ -521,13 +614,14 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     // ---- stage this k-range of x: permuted element order, fp16, high-nibble slots / 16;
     //      and the zero-point terms -8 * xsum * 2^-24 as float32
     griddep_wait();   // x may be the previous kernel's output; out / workspace may still be in its use
+    // Only the k tiles this CTA will actually visit are staged, in visiting order: its tile range
+    // starts at tile ks0 of a row block and wraps around the k-range, so it touches
+    // min(n_tiles, S_kr) tiles and the i-th tile it streams uses slot i mod that.
+    const int need_tiles = n_tiles < S_kr ? n_tiles : S_kr;
     {
-      // Only the k tiles this CTA will actually visit are staged: its tile range starts at tile ks0
-      // of a row block and wraps around the k-range, so it touches min(n_tiles, S_kr) tiles.  One warp
-      // instruction covers one (visited tile, row m): lane = octet (8 consecutive k) of the tile.
+      // One warp instruction covers one (visited tile, row m): lane = octet (8 consecutive k) of the tile.
       uint4* xs = reinterpret_cast<uint4*>(smem + L.xs);
       float* zps = reinterpret_cast<float*>(smem + L.zps);
-      const int need_tiles = n_tiles < S_kr ? n_tiles : S_kr;
       const long long kbase = static_cast<long long>(kr) * p.S * KT;
       int tile_i = 0, m = warp;
       while (m >= p.M) { m -= p.M; ++tile_i; }
@@ -541,7 +635,7 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
           ok[u] = tile_i < need_tiles;
           int ks = ks0 + tile_i;
           if (ks >= S_kr) ks -= S_kr;
-          mm[u] = m; kk[u] = ks;
+          mm[u] = m; kk[u] = tile_i;
           raw[u] = make_uint4(0u, 0u, 0u, 0u);
           const long long kpos = kbase + static_cast<long long>(ks) * KT + 8 * lane;
           if (ok[u] && (!RAGGED || kpos < p.K))
@@ -630,8 +724,8 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     bool dead = false;
     int rb = rb0;
     int seg = S_kr - ks0;                    // tiles until the end of row block rb (inside this k-range)
-    uint32_t x_off = static_cast<uint32_t>(ks0 * (GT * MPAD * 64));   // byte offsets of the current k tile in xs / zps
-    uint32_t z_off = static_cast<uint32_t>(ks0 * (GT * ZQB));
+    uint32_t x_off = 0, z_off = 0;           // byte offsets of the current k tile's slot in xs / zps
+    const uint32_t x_wrap = static_cast<uint32_t>(need_tiles * (GT * MPAD * 64));
     uint32_t so = 0;                         // byte offset of the current stage
     uint32_t full_a = bar_addr, empty_a = bar_addr + 8 * NSTAGES;
     uint32_t ph = 0;
@@ -642,14 +736,16 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
       // the row block is written directly if this CTA produces all of it
       const unsigned rb_t0 = static_cast<unsigned>(rb) * S_kr;
       const bool whole = p.n_kr == 1 && rb_t0 >= t0 && rb_t0 + S_kr <= t0 + n_tiles;
-      // Ahead of a flush through scratch: read the row group's counter now, so the round trip to
-      // L2 runs under the segment's math.  (A value read early stays valid: the counter only grows
-      // until the last contributor resets it.)
+      // Ahead of a flush through scratch: read the row group's counter while the segment's last tile
+      // is still to be computed, so the round trip to L2 runs under that tile's math and the value is
+      // as fresh as it can be for free.  (A value read early stays valid: the counter only grows until
+      // the last contributor resets it.)
       int seen = -1;
-      if (part == 0 && !whole && lane == 0)
-        seen = *reinterpret_cast<volatile int*>(p.counters + rb * COUNTERS_PER_RB + rg);
+      const bool want_seen = !CL && part == 0 && !whole && lane == 0;
 #pragma unroll 1
       for (int i = 0; i < seg; ++i) {
+        if (want_seen && i == seg - 1)
+          seen = *reinterpret_cast<volatile int*>(p.counters + rb * COUNTERS_PER_RB + rg);
         const bool ok = !dead && (mbar_try_wait_a(full_a, ph) || mbar_wait_slow(full_a, ph, abort_addr));
         if (ok) {
           // scales of the lane's four rows (slab 0: g, g+8; slab 1: g+16, g+24) for the warp's groups
@@ -716,6 +812,7 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
         if (lane == 0) mbar_arrive_a(empty_a);   // also in the dead state, so the producer never stalls on us
         x_off += GT * MPAD * 64;
         z_off += GT * ZQB;
+        if (x_off == x_wrap) { x_off = 0; z_off = 0; }
         so += STAGE_BYTES; full_a += 8; empty_a += 8;
         if (so == NSTAGES * STAGE_BYTES) { so = 0; full_a = bar_addr; empty_a = bar_addr + 8 * NSTAGES; ph ^= 1; }
       }
@@ -766,10 +863,51 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
           }
           __threadfence_block();
           named_bar_arrive(BAR_FREE0 + rg, PARTS * 32);
-          flush_row_group<MT, NC>(p, y, rb, rg, g, t4, lane, whole, seen, info);
+          if (CL) {
+            const uint32_t crank = cluster_ctarank();
+            const uint32_t red_bar = bar_addr + 8 * (2 * NSTAGES + rg);
+            constexpr int SLOT = red_slot_bytes(MT);
+            if (crank != 0) {
+              cluster_wait();                                   // the leader runs and its barriers exist
+              const uint32_t local = sbase + static_cast<uint32_t>(L.red + ((crank - 1) * NRG + rg) * SLOT + lane * 4);
+              const uint32_t dst = map_to_rank(local, 0);
+#pragma unroll
+              for (int sl = 0; sl < 2; ++sl) {
+#pragma unroll
+                for (int jm = 0; jm < MT; ++jm) {
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    if (NC == 2 || (e & 1) == 0) st_cluster_f32(dst + ((sl * MT + jm) * 4 + e) * 128, y[sl][jm][e]);
+                  }
+                }
+              }
+              mbar_arrive_remote(map_to_rank(red_bar, 0));
+            } else {
+              if (!mbar_wait_cluster_bounded(red_bar, 0)) {
+                if (lane == 0) { info->abort = 1; atomicExch(&g_device_status, 4); }
+              } else {
+                for (int r = 1; r < p.cluster; ++r) {          // rank order: the same bits every run
+                  const uint32_t src = sbase + static_cast<uint32_t>(L.red + ((r - 1) * NRG + rg) * SLOT + lane * 4);
+#pragma unroll
+                  for (int sl = 0; sl < 2; ++sl) {
+#pragma unroll
+                    for (int jm = 0; jm < MT; ++jm) {
+#pragma unroll
+                      for (int e = 0; e < 4; ++e) {
+                        if (NC == 2 || (e & 1) == 0) y[sl][jm][e] += __uint_as_float(lds32(src + ((sl * MT + jm) * 4 + e) * 128));
+                      }
+                    }
+                  }
+                }
+                flush_row_group<MT, NC>(p, y, rb, rg, g, t4, lane, true, -1, info);
+              }
+            }
+          } else {
+            flush_row_group<MT, NC>(p, y, rb, rg, g, t4, lane, whole, seen, info);
+          }
         }
       }
-      ++rb; seg = S_kr; x_off = 0; z_off = 0;   // the next segment starts a row block
+      ++rb; seg = S_kr;   // the next segment starts a row block
     }
   }
   __syncthreads();
@@ -781,6 +919,7 @@ struct Plan {
   int grid;
   int MT, MPAD;
   bool ragged;
+  bool cluster;             // cluster mode (p.cluster CTAs per row block), no scratch
   bool fits_32bit;          // the device-side schedule arithmetic is 32-bit
   size_t smem_bytes;
   size_t counters_bytes;   // COUNTER_BYTES, the same for every problem
@@ -806,6 +945,12 @@ inline int whole_row_block_tiles() {
   return v;
 }
 
+// Cluster mode can be switched off with LCQ_GEMV_CLUSTER=0 (read once).
+inline bool cluster_mode_enabled() {
+  static const bool on = [] { const char* e = getenv("LCQ_GEMV_CLUSTER"); return !(e && e[0] == '0'); }();
+  return on;
+}
+
 inline Plan make_plan(int M, int N, int K, int sm_count) {
   Plan pl;
   memset(&pl, 0, sizeof(pl));
@@ -816,7 +961,7 @@ inline Plan make_plan(int M, int N, int K, int sm_count) {
   pl.ragged = (K % KT) != 0;
   const int nstages = pl.MT == 1 ? Cfg<1>::NSTAGES : Cfg<2>::NSTAGES;
   const int ctas_per_sm = pl.MT == 1 ? Cfg<1>::CTAS_PER_SM : Cfg<2>::CTAS_PER_SM;
-  const int fixed = smem_layout(nstages, pl.MPAD, pl.MT, 0).total;
+  const int fixed = smem_layout(nstages, pl.MPAD, pl.MT, 0, 1).total;
   const int xc_bytes = max_dynamic_smem(ctas_per_sm) - fixed - 64;
   p.n_rb = (N + ROWS - 1) / ROWS;
   p.nst = (K + KT - 1) / KT;
@@ -826,11 +971,36 @@ inline Plan make_plan(int M, int N, int K, int sm_count) {
   p.n_kr = (p.nst + p.S - 1) / p.S;           // drop empty trailing ranges
   p.ctas_per_kr = (sm_count * ctas_per_sm) / p.n_kr;
   if (p.ctas_per_kr < 1) p.ctas_per_kr = 1;
-  const long long T = static_cast<long long>(p.n_rb) * p.S;
+  long long T = static_cast<long long>(p.n_rb) * p.S;
   if (p.ctas_per_kr > T) p.ctas_per_kr = static_cast<int>(T);
-  // Small problems (fewer than a few tiles per CTA): give each row block to c CTAs, c as small as
-  // keeps a CTA's share of a row block within whole_row_block_tiles(); c = 1 means no scratch at all.
-  if (T < 4LL * p.ctas_per_kr) {
+  p.x_tiles = p.S;
+  p.cluster = 1;
+  // Small problems (fewer than a few tiles per CTA): a cluster of c CTAs per row block, c the
+  // largest power of two (<= 8) that keeps every cluster resident at once, gives every CTA a tile and
+  // fits in shared memory.  A CTA then stages only its own share of x, so K needs no ranges.
+  const long long capacity = static_cast<long long>(sm_count) * ctas_per_sm;
+  if (static_cast<long long>(p.n_rb) * p.nst < 4LL * capacity && cluster_mode_enabled()) {
+    const int nst_cl = nstages_for(pl.MT, true);
+    int c = 8;
+    while (c > 1) {
+      const bool resident = static_cast<long long>(p.n_rb) * c <= capacity;
+      const int xt = (p.nst + c - 1) / c;
+      if (c <= p.nst && resident && smem_layout(nst_cl, pl.MPAD, pl.MT, xt, c).total <= max_dynamic_smem(ctas_per_sm)) break;
+      c >>= 1;
+    }
+    if (c > 1) {
+      pl.cluster = true;
+      p.cluster = c;
+      p.n_kr = 1;
+      p.S = p.nst;
+      p.x_tiles = (p.nst + c - 1) / c;
+      p.ctas_per_kr = p.n_rb * c;
+    }
+  }
+  T = static_cast<long long>(p.n_rb) * p.S;
+  // Otherwise: give each row block to c CTAs, c as small as keeps a CTA's share of a row block within
+  // whole_row_block_tiles(); c = 1 means no scratch at all.
+  if (!pl.cluster && T < 4LL * p.ctas_per_kr) {
     const int lim = whole_row_block_tiles();
     int c = (p.S + lim - 1) / lim;
     long long want = static_cast<long long>(p.n_rb) * c;
@@ -848,16 +1018,16 @@ inline Plan make_plan(int M, int N, int K, int sm_count) {
   p.max_split = max_split;
   pl.grid = p.n_kr * p.ctas_per_kr;
   pl.fits_32bit = (T + 1) * static_cast<long long>(p.ctas_per_kr) < (1LL << 32);
-  pl.smem_bytes = smem_layout(nstages, pl.MPAD, pl.MT, p.S).total;
+  pl.smem_bytes = smem_layout(nstages_for(pl.MT, pl.cluster), pl.MPAD, pl.MT, p.x_tiles, p.cluster).total;
   pl.counters_bytes = COUNTER_BYTES;
   pl.workspace_bytes = pl.counters_bytes +
                        static_cast<size_t>(p.n_rb) * p.n_kr * p.max_split * M * ROWS * sizeof(float);
   return pl;
 }
 
-template <int MT, int MPAD, bool RAGGED>
-int launch_t(const Plan& pl, const CUtensorMap& tw, const CUtensorMap& ts, bool allow_pdl, cudaStream_t stream) {
-  auto kern = w4a16_gemv_kernel<MT, MPAD, RAGGED>;
+template <int MT, int MPAD, bool RAGGED, bool CL>
+int launch_c(const Plan& pl, const CUtensorMap& tw, const CUtensorMap& ts, bool allow_pdl, cudaStream_t stream) {
+  auto kern = w4a16_gemv_kernel<MT, MPAD, RAGGED, CL>;
   static thread_local int configured_device = -1;  // per (thread, template instance)
   int dev = 0;
   LCQ_CUDA_TRY(cudaGetDevice(&dev));
@@ -874,13 +1044,30 @@ int launch_t(const Plan& pl, const CUtensorMap& tw, const CUtensorMap& ts, bool 
   cfg.blockDim = dim3((Cfg<MT>::NCW + 1) * 32);
   cfg.dynamicSmemBytes = pl.smem_bytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  if (CL) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = pl.p.cluster;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+  }
+  if (allow_pdl && pdl_enabled()) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = (allow_pdl && pdl_enabled()) ? 1 : 0;
+  cfg.numAttrs = n_attr;
   LCQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tw, ts, pl.p));
   return LCQ_OK;
+}
+
+template <int MT, int MPAD, bool RAGGED>
+int launch_t(const Plan& pl, const CUtensorMap& tw, const CUtensorMap& ts, bool allow_pdl, cudaStream_t stream) {
+  return pl.cluster ? launch_c<MT, MPAD, RAGGED, true>(pl, tw, ts, allow_pdl, stream)
+                    : launch_c<MT, MPAD, RAGGED, false>(pl, tw, ts, allow_pdl, stream);
 }
 
 template <bool RAGGED>

@@ -398,6 +398,14 @@ int lcq_gemv_tc_plan_check(int M, int N, int K, int sm_count, int* fields) {
     const long long t0 = gemv_tc::tile_begin(s, j), t1 = gemv_tc::tile_begin(s, j + 1);
     if (!pl.fits_32bit) { set_error("plan check: schedule does not fit 32 bits"); return LCQ_ERR_UNSUPPORTED; }
     if (t1 <= t0) { set_error("plan check: CTA %d has no tiles", b); return LCQ_ERR_BAD_ARG; }
+    if (pl.cluster) {
+      // cluster mode: the c CTAs of a cluster share one row block, nobody idles, a share fits the x slots
+      if (s.G != pl.grid || pl.grid % p.cluster != 0 || t0 / s.S_kr != b / p.cluster || (t1 - 1) / s.S_kr != b / p.cluster ||
+          t1 - t0 > p.x_tiles) {
+        set_error("plan check: CTA %d breaks the cluster layout", b);
+        return LCQ_ERR_BAD_ARG;
+      }
+    }
     int last_rb = -1;
     for (long long t = t0; t < t1; ++t) {
       const int rb = static_cast<int>(t / s.S_kr), ks = static_cast<int>(t % s.S_kr);
@@ -644,6 +652,116 @@ int lcq_quantize_int8(const void* w, void* w_int8, void* scales, int64_t N, int6
 int lcq_set_wait_limit_ns(unsigned long long limit_ns) {
   if (limit_ns == 0) { set_error("lcq_set_wait_limit_ns: the limit must be positive"); return LCQ_ERR_BAD_ARG; }
   LCQ_CUDA_TRY(cudaMemcpyToSymbol(g_wait_limit_ns, &limit_ns, sizeof(limit_ns)));
+  return LCQ_OK;
+}
+
+// ---------------------------------------------------------------- sharding context (one per rank)
+struct lcq_shard_ctx {
+  int rank, world, device;
+  size_t max_slice_bytes;
+  void* mine[2];                         // this rank's two regions (used alternately)
+  void* regions[2][peer::MAX_RANKS];     // every rank's regions as mapped here
+  int* state;                            // 2 x 2 ints
+  void* y_local;                         // this rank's [M, N/world] before the gather
+  void* workspace;
+  size_t workspace_bytes;
+  unsigned next;                         // which region the next call uses
+  bool connected;
+};
+
+int lcq_shard_ctx_create(int rank, int world, size_t max_slice_bytes, lcq_shard_ctx** out, unsigned char* handles128) {
+  if (!out || !handles128 || world < 1 || world > peer::MAX_RANKS || rank < 0 || rank >= world || max_slice_bytes == 0) {
+    set_error("lcq_shard_ctx_create: bad argument (world must be 1..%d)", peer::MAX_RANKS);
+    return LCQ_ERR_BAD_ARG;
+  }
+  max_slice_bytes = (max_slice_bytes + 15) & ~static_cast<size_t>(15);
+  lcq_shard_ctx* c = new lcq_shard_ctx();
+  memset(c, 0, sizeof(*c));
+  c->rank = rank; c->world = world; c->max_slice_bytes = max_slice_bytes;
+  LCQ_CUDA_TRY(cudaGetDevice(&c->device));
+  const size_t region_bytes = lcq_peer_region_bytes(max_slice_bytes, world);
+  for (int i = 0; i < 2; ++i) {
+    int rc = lcq_peer_alloc(region_bytes, &c->mine[i], handles128 + 64 * i);
+    if (rc != LCQ_OK) { lcq_shard_ctx_destroy(c); return rc; }
+    c->regions[i][rank] = c->mine[i];
+  }
+  cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->state), 4 * sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(c->state, 0, 4 * sizeof(int));
+  if (e == cudaSuccess) e = cudaMalloc(&c->y_local, max_slice_bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) { lcq_shard_ctx_destroy(c); return cuda_fail(e, "lcq_shard_ctx_create"); }
+  c->connected = world == 1;
+  *out = c;
+  return LCQ_OK;
+}
+
+int lcq_shard_ctx_connect(lcq_shard_ctx* c, const unsigned char* all_handles) {
+  if (!c || !all_handles) { set_error("lcq_shard_ctx_connect: bad argument"); return LCQ_ERR_BAD_ARG; }
+  for (int r = 0; r < c->world; ++r) {
+    if (r == c->rank) continue;
+    for (int i = 0; i < 2; ++i) {
+      int rc = lcq_peer_open(all_handles + (static_cast<size_t>(r) * 2 + i) * 64, &c->regions[i][r]);
+      if (rc != LCQ_OK) return rc;
+    }
+  }
+  c->connected = true;
+  return LCQ_OK;
+}
+
+int lcq_sharded_matmul_int4(lcq_shard_ctx* c, const void* x, const void* w_local, const void* scales_local, void** gathered,
+                            int M, int N_total, int K, int group_size, int x_dtype, int scale_dtype, int out_dtype,
+                            int algo, void* stream) {
+  if (!c || !gathered) { set_error("lcq_sharded_matmul_int4: bad argument"); return LCQ_ERR_BAD_ARG; }
+  if (!c->connected) { set_error("lcq_sharded_matmul_int4: call lcq_shard_ctx_connect first"); return LCQ_ERR_BAD_ARG; }
+  if (N_total <= 0 || N_total % c->world != 0 || M <= 0) {
+    set_error("lcq_sharded_matmul_int4: N_total=%d must be a positive multiple of the %d ranks", N_total, c->world);
+    return LCQ_ERR_BAD_ARG;
+  }
+  const int n_local = N_total / c->world;
+  const size_t slice = static_cast<size_t>(M) * n_local * (out_dtype == LCQ_F32 ? 4 : 2);
+  if (slice > c->max_slice_bytes || slice % 16 != 0) {
+    set_error("lcq_sharded_matmul_int4: slice of %zu bytes (limit %zu, must be a multiple of 16)", slice, c->max_slice_bytes);
+    return LCQ_ERR_BAD_ARG;
+  }
+  const size_t need = lcq_matmul_workspace_bytes(4, M, n_local, K, group_size, x_dtype, scale_dtype, out_dtype, algo);
+  if (need == static_cast<size_t>(-1)) { set_error("lcq_sharded_matmul_int4: no kernel covers this problem"); return LCQ_ERR_UNSUPPORTED; }
+  if (need > c->workspace_bytes) {       // first call of this size only: allocates and synchronises the device
+    LCQ_CUDA_TRY(cudaDeviceSynchronize());
+    if (c->workspace) LCQ_CUDA_TRY(cudaFree(c->workspace));
+    c->workspace = nullptr; c->workspace_bytes = 0;
+    LCQ_CUDA_TRY(cudaMalloc(&c->workspace, need));
+    LCQ_CUDA_TRY(cudaMemset(c->workspace, 0, need));
+    LCQ_CUDA_TRY(cudaDeviceSynchronize());
+    c->workspace_bytes = need;
+  }
+  const unsigned i = c->next & 1u;
+  uint8_t* data = static_cast<uint8_t*>(c->mine[i]) + peer::FLAG_BYTES;
+  void* y = c->world == 1 ? static_cast<void*>(data) : c->y_local;
+  int rc = lcq_matmul_int4(x, w_local, scales_local, y, M, n_local, K, group_size, x_dtype, scale_dtype, out_dtype, algo,
+                           c->workspace, c->workspace_bytes, stream);
+  if (rc != LCQ_OK) return rc;
+  if (c->world > 1) {
+    rc = lcq_allgather_push(y, slice, c->regions[i], c->rank, c->world, c->state + 2 * i, stream);
+    if (rc != LCQ_OK) return rc;
+  }
+  c->next++;
+  *gathered = data;
+  return LCQ_OK;
+}
+
+int lcq_shard_ctx_destroy(lcq_shard_ctx* c) {
+  if (!c) return LCQ_OK;
+  cudaDeviceSynchronize();
+  for (int i = 0; i < 2; ++i) {
+    for (int r = 0; r < c->world; ++r)
+      if (r != c->rank && c->regions[i][r]) cudaIpcCloseMemHandle(c->regions[i][r]);
+    if (c->mine[i]) cudaFree(c->mine[i]);
+  }
+  if (c->state) cudaFree(c->state);
+  if (c->y_local) cudaFree(c->y_local);
+  if (c->workspace) cudaFree(c->workspace);
+  (void)cudaGetLastError();
+  delete c;
   return LCQ_OK;
 }
 

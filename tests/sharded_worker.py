@@ -55,6 +55,39 @@ def main():
         if _lib.lib().lcq_check_device_status(None) != 0:
             failures.append((gather, "device status", _lib.lib().lcq_last_error().decode()))
         layer.close()
+    # ---- the same through the C-ABI sharding context (what a host without Python would call)
+    import ctypes
+    lib = _lib.lib()
+    n_local = n // world
+    ctx = ctypes.c_void_p()
+    handles = ctypes.create_string_buffer(128)
+    _lib.check(lib.lcq_shard_ctx_create(rank, world, 16 * n_local * 2, ctypes.byref(ctx), handles))
+    gathered_handles = [None] * world
+    dist.all_gather_object(gathered_handles, handles.raw)
+    dist.barrier()                                           # every context exists before anyone connects
+    _lib.check(lib.lcq_shard_ctx_connect(ctx, b"".join(gathered_handles)))
+    dist.barrier()
+    w_loc, s_loc = wd[rank * n_local:(rank + 1) * n_local], sd[rank * n_local:(rank + 1) * n_local]
+    st = torch.cuda.current_stream().cuda_stream
+    for m in (1, 16):
+        for call, xh in enumerate(xs):
+            x = torch.from_numpy(np.ascontiguousarray(xh[:m])).to(dev)
+            out_ptr = ctypes.c_void_p()
+            _lib.check(lib.lcq_sharded_matmul_int4(ctx, x.data_ptr(), w_loc.data_ptr(), s_loc.data_ptr(), ctypes.byref(out_ptr),
+                                                   m, n, k, 32, _lib.F16, _lib.F16, _lib.F16, _lib.ALGO_AUTO, st))
+            torch.cuda.synchronize()
+            class _Mem:                                   # zero-copy view of the device pointer the library returned
+                __cuda_array_interface__ = {"shape": (world * m * n_local,), "typestr": "<f2",
+                                            "data": (out_ptr.value, True), "version": 3}
+            host = torch.as_tensor(_Mem(), device=dev).cpu().numpy().reshape(world, m, n_local)
+            got = host.transpose(1, 0, 2).reshape(m, n).astype(np.float32)
+            ref = O.matmul_int4(xh[:m].astype(np.float32), wp, s, 32)
+            if np.any(np.abs(got - ref) > 1e-2 + 1e-2 * np.abs(ref)):
+                failures.append(("c-abi ctx", m, call, float(np.abs(got - ref).max())))
+    if lib.lcq_check_device_status(None) != 0:
+        failures.append(("c-abi ctx", "device status"))
+    dist.barrier()
+    _lib.check(lib.lcq_shard_ctx_destroy(ctx))
     ok = torch.tensor([0 if failures else 1], device=dev)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     print(f"rank {rank}: {'SHARDED_OK' if not failures else 'SHARDED_FAIL ' + repr(failures[:6])}", flush=True)
