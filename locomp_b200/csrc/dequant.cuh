@@ -203,9 +203,9 @@ __global__ void __launch_bounds__(256) dequant_w8_elems_kernel(const int8_t* __r
 
 // Blocks of `kern` (256 threads, no dynamic shared memory) that are resident on the whole GPU at
 // once: the grid-stride kernels are launched with exactly one wave, never more blocks than work.
-template <typename Kern>
-int one_wave_grid(Kern kern, long long work_items, int per_block, int sm_count) {
-  static thread_local int per_sm = 0;      // per (thread, kernel instance)
+template <auto kern>
+int one_wave_grid(long long work_items, int per_block, int sm_count) {
+  static thread_local int per_sm = 0;      // per (thread, kernel): the kernel is a template VALUE, not its type
   if (per_sm == 0) {
     int nb = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, 256, 0) != cudaSuccess || nb < 1) nb = 4;
@@ -230,12 +230,12 @@ int launch_dequant(int wbits, const void* w, const void* scales, void* out, long
     if (fast) {
       const long long words = total / 8;
       // 8 warps per block, each taking DQ_UNROLL blocks of 32 words per iteration
-      const int grid = one_wave_grid(dequant_w4_words_kernel<ST, OT>, (words + 31) / 32, 8 * DQ_UNROLL, sm_count);
+      const int grid = one_wave_grid<dequant_w4_words_kernel<ST, OT>>((words + 31) / 32, 8 * DQ_UNROLL, sm_count);
       dequant_w4_words_kernel<ST, OT><<<grid, 256, 0, stream>>>(
           static_cast<const uint32_t*>(w), static_cast<const ST*>(scales), static_cast<OT*>(out), words, G, gshift);
     } else {
       const long long bytes = total / 2;
-      const int grid = one_wave_grid(dequant_w4_bytes_kernel<ST, OT>, bytes, 256, sm_count);
+      const int grid = one_wave_grid<dequant_w4_bytes_kernel<ST, OT>>(bytes, 256, sm_count);
       dequant_w4_bytes_kernel<ST, OT><<<grid, 256, 0, stream>>>(
           static_cast<const uint8_t*>(w), static_cast<const ST*>(scales), static_cast<OT*>(out), bytes,
           static_cast<int>(K), G);
@@ -244,11 +244,11 @@ int launch_dequant(int wbits, const void* w, const void* scales, void* out, long
     const bool fast = (K % 4 == 0) && (G % 4 == 0) && aligned(w, 4) && aligned(out, out_vec_align);
     if (fast) {
       const long long words = total / 4;
-      const int grid = one_wave_grid(dequant_w8_words_kernel<ST, OT>, words, 256 * DQ_UNROLL, sm_count);
+      const int grid = one_wave_grid<dequant_w8_words_kernel<ST, OT>>(words, 256 * DQ_UNROLL, sm_count);
       dequant_w8_words_kernel<ST, OT><<<grid, 256, 0, stream>>>(
           static_cast<const uint32_t*>(w), static_cast<const ST*>(scales), static_cast<OT*>(out), words, G, gshift);
     } else {
-      const int grid = one_wave_grid(dequant_w8_elems_kernel<ST, OT>, total, 256, sm_count);
+      const int grid = one_wave_grid<dequant_w8_elems_kernel<ST, OT>>(total, 256, sm_count);
       dequant_w8_elems_kernel<ST, OT><<<grid, 256, 0, stream>>>(
           static_cast<const int8_t*>(w), static_cast<const ST*>(scales), static_cast<OT*>(out), total,
           static_cast<int>(K), G);

@@ -625,7 +625,7 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
       const long long kbase = static_cast<long long>(kr) * p.S * KT;
       int tile_i = 0, m = warp;
       while (m >= p.M) { m -= p.M; ++tile_i; }
-      constexpr int U = 4;   // independent 16-byte loads in flight per lane
+      constexpr int U = MT == 2 ? 8 : 4;   // independent 16-byte loads in flight per lane
       while (tile_i < need_tiles) {
         uint4 raw[U];
         int mm[U], kk[U];

@@ -78,7 +78,7 @@ def main():
             torch.cuda.synchronize()
             class _Mem:                                   # zero-copy view of the device pointer the library returned
                 __cuda_array_interface__ = {"shape": (world * m * n_local,), "typestr": "<f2",
-                                            "data": (out_ptr.value, True), "version": 3}
+                                            "data": (out_ptr.value, False), "version": 3}
             host = torch.as_tensor(_Mem(), device=dev).cpu().numpy().reshape(world, m, n_local)
             got = host.transpose(1, 0, 2).reshape(m, n).astype(np.float32)
             ref = O.matmul_int4(xh[:m].astype(np.float32), wp, s, 32)
