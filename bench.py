@@ -254,6 +254,37 @@ def run_profile_shape(args):
                       "weight_gbs": weight_bytes(k, n) / us / 1e3, "tflops": 2.0 * m * n * k / us / 1e6}), flush=True)
 
 
+def run_profile_dequant(args):
+    """A handful of launches of lcq_dequant_int4 on the 4096 x 14336 weight (-> float32): the small
+    case an `ncu` capture of the dequantize kernel wants.  Three rotating buffer sets (800 MB)."""
+    import torch
+    from locomp_b200 import _lib
+    lib = _lib.lib()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    n, k = 4096, 14336
+    g = torch.Generator(device=dev).manual_seed(5)
+    ws = [torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev, generator=g) for _ in range(3)]
+    ss = [(torch.randn(n, k // GROUP, device=dev, generator=g).abs() * 0.02).half() for _ in range(3)]
+    outs = [torch.empty(n, k, dtype=torch.float32, device=dev) for _ in range(3)]
+
+    def launch(i):
+        _lib.check(lib.lcq_dequant_int4(ws[i % 3].data_ptr(), ss[i % 3].data_ptr(), outs[i % 3].data_ptr(), n, k, GROUP,
+                                        _lib.F16, _lib.F32, None))
+    for i in range(args.warmup):
+        launch(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        launch(args.warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    moved = n * k // 2 + n * (k // GROUP) * 2 + 4 * n * k
+    print(json.dumps({"profile_dequant": {"N": n, "K": k, "out": "f32"}, "us_per_launch": us, "gbs_moved": moved / us / 1e3}), flush=True)
+
+
 def run_ours(args, rank: int, world: int, local_rank: int):
     import torch
     import locomp_b200 as L
@@ -546,6 +577,7 @@ def main():
     ap.add_argument("--watchdog", type=int, default=900, help="abort the process after this many seconds")
     ap.add_argument("--profile-shape", default=None, metavar="KxNxM",
                     help="run a few launches of one problem and exit (small case for ncu captures)")
+    ap.add_argument("--profile-dequant", action="store_true", help="a few launches of the dequantize kernel, for ncu")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="headline only: skip the cfg1/cfg3/cfg4/cfg5/dequant blocks")
     args = ap.parse_args()
@@ -565,6 +597,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.profile_dequant:
+        run_profile_dequant(args)
         return
     if args.profile_shape:
         run_profile_shape(args)
