@@ -62,10 +62,13 @@ template <> struct Out8<float> {
   static __device__ __forceinline__ void store(float*, const float (&)[8]) {}   // never taken: float32 goes through Out4
 };
 
-constexpr int DQ_UNROLL = 4;   // independent 128-byte warp loads in flight per warp
+// Independent 128-byte warp loads in flight per warp, as measured best on a 4096 x 14336 weight:
+// int4 -> f32 4, int4 -> 16-bit 2, int8 1 (more only costs registers, hence resident blocks).
+template <typename OT> __host__ __device__ constexpr int dq4_unroll() { return sizeof(OT) == 4 ? 4 : 2; }
+constexpr int DQ8_UNROLL = 1;
 
 // ---- int4 fast path: K % 8 == 0, G % 8 == 0, w 4-byte aligned, out 16-byte aligned.
-// total_words = N*K/8.  A warp iteration covers DQ_UNROLL blocks of 32 words (256 weights each): all
+// total_words = N*K/8.  A warp iteration covers dq4_unroll<OT>() blocks of 32 words (256 weights each): all
 // loads of weights and scales are issued before the first store.  float32 output: two shuffles hand
 // every lane 4 consecutive weights per store, so a store instruction writes 512 contiguous bytes.
 // 16-bit output: a lane's own word is 8 outputs = 16 bytes, contiguous across the warp as it is.
@@ -75,6 +78,7 @@ __global__ void __launch_bounds__(256) dequant_w4_words_kernel(const uint32_t* _
                                                                OT* __restrict__ out,
                                                                long long total_words, int G, int gshift) {
   constexpr bool WIDE = sizeof(OT) == 4;
+  constexpr int DQ_UNROLL = dq4_unroll<OT>();
   constexpr int NS = WIDE ? 2 : 1;              // stores (and scales) per lane and block
   const int lane = threadIdx.x & 31;
   const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -156,25 +160,25 @@ __device__ __forceinline__ void int8x4_to_f32(uint32_t v, float (&f)[4]) {
 }
 
 // ---- int8 fast path: K % 4 == 0, G % 4 == 0; one 32-bit word (4 weights) per thread and load,
-// DQ_UNROLL loads in flight.
+// DQ8_UNROLL loads in flight.
 template <typename ST, typename OT>
 __global__ void __launch_bounds__(256) dequant_w8_words_kernel(const uint32_t* __restrict__ w,
                                                                const ST* __restrict__ scales,
                                                                OT* __restrict__ out,
                                                                long long total_words, int G, int gshift) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total_words; i0 += stride * DQ_UNROLL) {
-    uint32_t word[DQ_UNROLL];
-    float sc[DQ_UNROLL];
+  for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total_words; i0 += stride * DQ8_UNROLL) {
+    uint32_t word[DQ8_UNROLL];
+    float sc[DQ8_UNROLL];
 #pragma unroll
-    for (int u = 0; u < DQ_UNROLL; ++u) {
+    for (int u = 0; u < DQ8_UNROLL; ++u) {
       const long long i = i0 + u * stride;
       const bool ok = i < total_words;
       word[u] = ok ? __ldg(w + i) : 0u;
       sc[u] = ok ? to_f32<ST>(__ldg(scales + scale_index(i * 4, G, gshift))) : 0.0f;
     }
 #pragma unroll
-    for (int u = 0; u < DQ_UNROLL; ++u) {
+    for (int u = 0; u < DQ8_UNROLL; ++u) {
       const long long i = i0 + u * stride;
       if (i < total_words) {
         float f[4];
@@ -229,8 +233,8 @@ int launch_dequant(int wbits, const void* w, const void* scales, void* out, long
     const bool fast = (K % 8 == 0) && (G % 8 == 0) && aligned(w, 4) && aligned(out, 16);
     if (fast) {
       const long long words = total / 8;
-      // 8 warps per block, each taking DQ_UNROLL blocks of 32 words per iteration
-      const int grid = one_wave_grid<dequant_w4_words_kernel<ST, OT>>((words + 31) / 32, 8 * DQ_UNROLL, sm_count);
+      // 8 warps per block, each taking dq4_unroll<OT>() blocks of 32 words per iteration
+      const int grid = one_wave_grid<dequant_w4_words_kernel<ST, OT>>((words + 31) / 32, 8 * dq4_unroll<OT>(), sm_count);
       dequant_w4_words_kernel<ST, OT><<<grid, 256, 0, stream>>>(
           static_cast<const uint32_t*>(w), static_cast<const ST*>(scales), static_cast<OT*>(out), words, G, gshift);
     } else {
@@ -244,7 +248,7 @@ int launch_dequant(int wbits, const void* w, const void* scales, void* out, long
     const bool fast = (K % 4 == 0) && (G % 4 == 0) && aligned(w, 4) && aligned(out, out_vec_align);
     if (fast) {
       const long long words = total / 4;
-      const int grid = one_wave_grid<dequant_w8_words_kernel<ST, OT>>(words, 256 * DQ_UNROLL, sm_count);
+      const int grid = one_wave_grid<dequant_w8_words_kernel<ST, OT>>(words, 256 * DQ8_UNROLL, sm_count);
       dequant_w8_words_kernel<ST, OT><<<grid, 256, 0, stream>>>(
           static_cast<const uint32_t*>(w), static_cast<const ST*>(scales), static_cast<OT*>(out), words, G, gshift);
     } else {

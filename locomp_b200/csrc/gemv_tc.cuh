@@ -158,6 +158,9 @@ __host__ __device__ inline SmemLayout smem_layout(int nstages, int MPAD, int MT,
 }
 
 __device__ __forceinline__ void store_out(void* out, int dtype, long long idx, float v) {
+#if defined(LCQ_EXPERIMENT) && LCQ_EXPERIMENT == 3
+  if (dtype != 12345) { if (v == 12345.678f) static_cast<float*>(out)[idx] = v; return; }
+#endif
   if (dtype == LCQ_F16) static_cast<__half*>(out)[idx] = __float2half_rn(v);
   else if (dtype == LCQ_BF16) static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
   else static_cast<float*>(out)[idx] = v;
@@ -274,6 +277,19 @@ __device__ __noinline__ bool mbar_wait_cluster_bounded(uint32_t bar, uint32_t pa
   }
 }
 
+// q - 8 as fp16 pairs without a conversion: (word & 0x000F000F) | 0x64006400 is {1024 + q, 1024 + q'},
+// minus {1032, 1032}; for nibbles in bits 4-7, {1024 + 16 q, ...} minus {1152, 1152} = 16 (q - 8).
+__device__ __forceinline__ uint32_t magic_lo(uint32_t w) {
+  uint32_t r;
+  asm("{\n\t.reg .b32 t;\n\tlop3.b32 t, %1, 0x000F000F, 0x64006400, 0xEA;\n\tsub.f16x2 %0, t, %2;\n\t}" : "=r"(r) : "r"(w), "r"(0x64086408u));
+  return r;
+}
+__device__ __forceinline__ uint32_t magic_hi(uint32_t w) {
+  uint32_t r;
+  asm("{\n\t.reg .b32 t;\n\tlop3.b32 t, %1, 0x00F000F0, 0x64006400, 0xEA;\n\tsub.f16x2 %0, t, %2;\n\t}" : "=r"(r) : "r"(w), "r"(0x64806480u));
+  return r;
+}
+
 // What one thread works out for the whole CTA before the first barrier (schedule arithmetic needs
 // several integer divisions; the other threads read the results from shared memory).
 struct CtaInfo {
@@ -305,6 +321,37 @@ struct SlotIter {
   }
 };
 
+// The row group's values are the outputs (this CTA, or this cluster, produced the whole row block):
+// store them.  Inline on purpose: an out-of-line call parks the caller's registers on the stack, and
+// with nearly all of L1 carved out as shared memory that round trip goes to L2 (about a microsecond
+// per call, measured); typed pointers keep the address arithmetic to one multiply per column.
+template <typename OT, int MT, int NC>
+__device__ __forceinline__ void store_row_group_t(OT* out, const Params& p, const float (&y)[2][MT][4], int n0, int t4) {
+  const bool rows_inside = n0 - (n0 & 7) + 32 <= p.N;      // the row group's 32 rows all exist
+#pragma unroll
+  for (int jm = 0; jm < MT; ++jm) {
+#pragma unroll
+    for (int e = 0; e < NC; ++e) {
+      const int m = 8 * jm + 2 * t4 + e;
+      if (m < p.M) {
+        OT* col = out + static_cast<long long>(m) * p.N + n0;
+#pragma unroll
+        for (int sl = 0; sl < 2; ++sl) {
+          if (rows_inside || n0 + 16 * sl < p.N) col[16 * sl] = from_f32<OT>(y[sl][jm][e]);
+          if (rows_inside || n0 + 16 * sl + 8 < p.N) col[16 * sl + 8] = from_f32<OT>(y[sl][jm][2 + e]);
+        }
+      }
+    }
+  }
+}
+template <int MT, int NC>
+__device__ __forceinline__ void store_row_group(const Params& p, const float (&y)[2][MT][4], int rb, int rg, int g, int t4) {
+  const int n0 = rb * ROWS + rg * 32 + g;               // rows n0 + 16*sl and n0 + 16*sl + 8
+  if (p.out_dtype == LCQ_F16) store_row_group_t<__half, MT, NC>(static_cast<__half*>(p.out), p, y, n0, t4);
+  else if (p.out_dtype == LCQ_BF16) store_row_group_t<__nv_bfloat16, MT, NC>(static_cast<__nv_bfloat16*>(p.out), p, y, n0, t4);
+  else store_row_group_t<float, MT, NC>(static_cast<float*>(p.out), p, y, n0, t4);
+}
+
 // Settles the 32 rows of one row group at the end of a CTA's share of a row block (called by the
 // row group's slice-0 warp with the slices already added up in y).  `whole`: the CTA produced the
 // entire row block, so the values are the outputs.  Otherwise the row block has several
@@ -313,7 +360,7 @@ struct SlotIter {
 // lane 0 read before the tile's math.  Kept out of line: it runs once per row block, and its
 // 64-bit index arithmetic should not cost the streaming loop registers.
 template <int MT, int NC>
-__device__ __noinline__ void flush_row_group(const Params& p, const float (&y)[2][MT][4], int rb, int rg, int g, int t4,
+__device__ __forceinline__ void flush_row_group(const Params& p, const float (&y)[2][MT][4], int rb, int rg, int g, int t4,
                                              int lane, bool whole, int seen_lane0, const CtaInfo* info) {
   const int n0 = rb * ROWS + rg * 32 + g;               // rows n0 + 16*sl and n0 + 16*sl + 8
   if (whole) {
@@ -503,6 +550,12 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
   constexpr int CPW = GT / PARTS;             // groups per warp and tile (4 or 2)
   constexpr int NC = MPAD == 1 ? 1 : 2;       // output columns a lane keeps per m tile (only column 0 exists at M == 1)
   constexpr int ZQB = zq_group_bytes(MPAD);
+  // MAGIC: the zero point is taken off the weights, not the accumulator.  (word & mask) | 0x6400 in a
+  // 16-bit lane is the fp16 number 1024 + q (1024 + 16 q for a nibble in bits 4-7); subtracting 1032
+  // (1152) leaves q - 8 (16 (q - 8)) exactly.  One more instruction per operand register, but no
+  // zero-point quad to fetch from shared memory per (group, m tile): worth it where shared-memory
+  // bandwidth, not issue rate, is the bound (two m tiles).
+  constexpr bool MAGIC = MT == 2;
   // Declared 1024-byte aligned (the 128-byte TMA swizzle needs it) and used directly, so the
   // compiler keeps every access in the shared address space with 32-bit addressing.
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -670,7 +723,7 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
             q.z = *reinterpret_cast<const uint32_t*>(&h2); q.w = *reinterpret_cast<const uint32_t*>(&h3);
             const int grp = kk[u] * GT + (lane >> 2);
             xs[(grp * MPAD + mm[u]) * 4 + (lane & 3)] = q;
-            if ((lane & 3) == 0) {
+            if (!MAGIC && (lane & 3) == 0) {
               // the MMA's accumulator-input quad of rows (g, g+8) x columns (m0, m1) is {z(m0), z(m1), z(m0), z(m1)}
               const float z = sum * -4.76837158203125e-7f;   // -8 * xsum * 2^-24
               if (MPAD == 1) {
@@ -696,6 +749,8 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
       }
     }
 
+    float zero4[4];
+    opaque_zero4(zero4);
     // All hot-loop operands are read with explicit shared-space loads from 32-bit addresses.
     // Word t4 of row (32*rg + g), this warp's group c, inside a stage: every row a lane reads has
     // (row & 7) == g, so the 128-byte swizzle is the same XOR for all four of them; the other three
@@ -779,9 +834,13 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
 #pragma unroll
             for (int jm = 0; jm < MT; ++jm) {
               bx[jm] = lds128(xa[jm] + c * (MPAD * 64));
-              const uint4 z = lds128(za + c * ZQB + jm * 64);
-              zc[jm][0] = __uint_as_float(z.x); zc[jm][1] = __uint_as_float(z.y);
-              zc[jm][2] = __uint_as_float(z.z); zc[jm][3] = __uint_as_float(z.w);
+              if (MAGIC) {
+                zc[jm][0] = zero4[0]; zc[jm][1] = zero4[1]; zc[jm][2] = zero4[2]; zc[jm][3] = zero4[3];
+              } else {
+                const uint4 z = lds128(za + c * ZQB + jm * 64);
+                zc[jm][0] = __uint_as_float(z.x); zc[jm][1] = __uint_as_float(z.y);
+                zc[jm][2] = __uint_as_float(z.z); zc[jm][3] = __uint_as_float(z.w);
+              }
             }
             const uint32_t wp = w_addr[c] + so;
 #pragma unroll
@@ -789,8 +848,14 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
               const uint32_t wa = lds32(wp + sl * 2048);
               const uint32_t wb = lds32(wp + sl * 2048 + 1024);
               const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
-              const uint32_t a0 = wa & 0x000F000Fu, a1 = wb & 0x000F000Fu, a2 = wa & 0x00F000F0u, a3 = wb & 0x00F000F0u;
-              const uint32_t b0 = wa8 & 0x000F000Fu, b1 = wb8 & 0x000F000Fu, b2 = wa8 & 0x00F000F0u, b3 = wb8 & 0x00F000F0u;
+              uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+              if (MAGIC) {
+                a0 = magic_lo(wa); a1 = magic_lo(wb); a2 = magic_hi(wa); a3 = magic_hi(wb);
+                b0 = magic_lo(wa8); b1 = magic_lo(wb8); b2 = magic_hi(wa8); b3 = magic_hi(wb8);
+              } else {
+                a0 = wa & 0x000F000Fu; a1 = wb & 0x000F000Fu; a2 = wa & 0x00F000F0u; a3 = wb & 0x00F000F0u;
+                b0 = wa8 & 0x000F000Fu; b1 = wb8 & 0x000F000Fu; b2 = wa8 & 0x00F000F0u; b3 = wb8 & 0x00F000F0u;
+              }
 #pragma unroll
               for (int jm = 0; jm < MT; ++jm) {
                 float d[4];
@@ -827,7 +892,7 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
 #pragma unroll
           for (int jm = 0; jm < MT; ++jm) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) { y[sl][jm][e] = acc[sl][jm][e] * 16777216.0f; acc[sl][jm][e] = 0.0f; }
+            for (int e = 0; e < 4; ++e) { y[sl][jm][e] = MAGIC ? acc[sl][jm][e] : acc[sl][jm][e] * 16777216.0f; acc[sl][jm][e] = 0.0f; }
           }
         }
         if (part != 0) {
@@ -899,11 +964,18 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
                     }
                   }
                 }
-                flush_row_group<MT, NC>(p, y, rb, rg, g, t4, lane, true, -1, info);
+                store_row_group<MT, NC>(p, y, rb, rg, g, t4);
               }
             }
           } else {
-            flush_row_group<MT, NC>(p, y, rb, rg, g, t4, lane, whole, seen, info);
+#if defined(LCQ_EXPERIMENT) && LCQ_EXPERIMENT == 1
+            if (y[0][0][0] == 12345.678f) flush_row_group<MT, NC>(p, y, rb, rg, g, t4, lane, whole, seen, info);
+#elif defined(LCQ_EXPERIMENT) && LCQ_EXPERIMENT >= 2
+            flush_row_group<MT, NC>(p, y, rb, rg, g, t4, lane, true, seen, info);
+#else
+            if (whole) store_row_group<MT, NC>(p, y, rb, rg, g, t4);
+            else flush_row_group<MT, NC>(p, y, rb, rg, g, t4, lane, false, seen, info);
+#endif
           }
         }
       }
