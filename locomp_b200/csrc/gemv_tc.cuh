@@ -158,9 +158,6 @@ __host__ __device__ inline SmemLayout smem_layout(int nstages, int MPAD, int MT,
 }
 
 __device__ __forceinline__ void store_out(void* out, int dtype, long long idx, float v) {
-#if defined(LCQ_EXPERIMENT) && LCQ_EXPERIMENT == 3
-  if (dtype != 12345) { if (v == 12345.678f) static_cast<float*>(out)[idx] = v; return; }
-#endif
   if (dtype == LCQ_F16) static_cast<__half*>(out)[idx] = __float2half_rn(v);
   else if (dtype == LCQ_BF16) static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
   else static_cast<float*>(out)[idx] = v;
@@ -968,14 +965,8 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
               }
             }
           } else {
-#if defined(LCQ_EXPERIMENT) && LCQ_EXPERIMENT == 1
-            if (y[0][0][0] == 12345.678f) flush_row_group<MT, NC>(p, y, rb, rg, g, t4, lane, whole, seen, info);
-#elif defined(LCQ_EXPERIMENT) && LCQ_EXPERIMENT >= 2
-            flush_row_group<MT, NC>(p, y, rb, rg, g, t4, lane, true, seen, info);
-#else
             if (whole) store_row_group<MT, NC>(p, y, rb, rg, g, t4);
             else flush_row_group<MT, NC>(p, y, rb, rg, g, t4, lane, false, seen, info);
-#endif
           }
         }
       }
