@@ -30,7 +30,14 @@
 // whose tiles were produced by more than one CTA is combined through scratch: every
 // contributor writes its float32 partial, bumps a counter (one per row block and row
 // group), and the last one sums all partials in a fixed order, writes the output and resets
-// the counter.  Nobody spins on another CTA.
+// the counter.  Nobody spins on another CTA.  At M > 8 (two m tiles) the zero point is
+// taken off the weights instead (see MAGIC in the kernel): shared-memory bandwidth bounds
+// that case, and it saves the fetch of the zero-point quads.
+//
+// Small problems (fewer than ~4 tiles per CTA) run in cluster mode: a thread-block cluster
+// of 2, 4 or 8 CTAs owns a row block, every CTA streams its share of the k tiles, and the
+// partial sums meet in the first CTA's shared memory (remote stores + remote mbarrier
+// arrivals over distributed shared memory) -- no scratch, no counters, no global round trip.
 //
 // Any K that is a multiple of 64: the last k tile may be partial (TMA fills the missing
 // bytes with zeros).  When K is not a multiple of 256 the scale rows are not 16-byte
@@ -287,6 +294,12 @@ __device__ __forceinline__ uint32_t magic_hi(uint32_t w) {
   return r;
 }
 
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 // What one thread works out for the whole CTA before the first barrier (schedule arithmetic needs
 // several integer divisions; the other threads read the results from shared memory).
 struct CtaInfo {
@@ -354,8 +367,9 @@ __device__ __forceinline__ void store_row_group(const Params& p, const float (&y
 // entire row block, so the values are the outputs.  Otherwise the row block has several
 // contributors (other CTAs of this k-range and / or other k-ranges): publish the partial, count,
 // and let the last contributor sum all partials in slot order.  `seen_lane0` is the counter value
-// lane 0 read before the tile's math.  Kept out of line: it runs once per row block, and its
-// 64-bit index arithmetic should not cost the streaming loop registers.
+// lane 0 read (with an acquire load) a tile earlier.  Inline on purpose: an out-of-line call parks
+// the caller's registers on the stack, and with nearly all of L1 carved out as shared memory that
+// round trip goes to L2 (about a microsecond per call, measured).
 template <int MT, int NC>
 __device__ __forceinline__ void flush_row_group(const Params& p, const float (&y)[2][MT][4], int rb, int rg, int g, int t4,
                                              int lane, bool whole, int seen_lane0, const CtaInfo* info) {
@@ -409,7 +423,9 @@ __device__ __forceinline__ void flush_row_group(const Params& p, const float (&y
   // output, without publishing (no global round trip at the kernel's tail).
   const int seen = __shfl_sync(0xffffffffu, seen_lane0, 0);
   if (seen == n_contrib - 1) {
-    __threadfence();
+    // (no fence here: lane 0 read the counter with an acquire load a tile ago, and the shuffle above
+    // orders the other lanes' loads after it)
+    __syncwarp();
     // One pass per contributor, in slot order (the reducer below uses the same order, so both paths
     // give the same bits); all of a pass's loads are independent and in flight together.
     float sum[2][MT][NC][2];
@@ -797,7 +813,7 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
 #pragma unroll 1
       for (int i = 0; i < seg; ++i) {
         if (want_seen && i == seg - 1)
-          seen = *reinterpret_cast<volatile int*>(p.counters + rb * COUNTERS_PER_RB + rg);
+          seen = ld_acquire_gpu(p.counters + rb * COUNTERS_PER_RB + rg);
         const bool ok = !dead && (mbar_try_wait_a(full_a, ph) || mbar_wait_slow(full_a, ph, abort_addr));
         if (ok) {
           // scales of the lane's four rows (slab 0: g, g+8; slab 1: g+16, g+24) for the warp's groups
