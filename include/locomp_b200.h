@@ -282,6 +282,13 @@ int lcq_set_wait_limit_ns(unsigned long long limit_ns);
  */
 int lcq_gemv_tc_plan_check(int M, int N, int K, int sm_count, int* fields);
 
+/*
+ * Host-only: CTAs per thread-block cluster the decode kernel would use for this problem on a GPU
+ * with sm_count SMs (1 = no clusters: stream-K with scratch, or whole row blocks per CTA; 2, 4 or 8 =
+ * cluster mode, partial sums meet in the first CTA's shared memory).  Negative: status code.
+ */
+int lcq_gemv_tc_plan_cluster(int M, int N, int K, int sm_count);
+
 #ifdef __cplusplus
 }
 #endif

@@ -54,6 +54,7 @@ SIGNATURES = {
     "lcq_check_device_status": (_c.c_int, [_c.c_void_p]),
     "lcq_set_wait_limit_ns": (_c.c_int, [_c.c_ulonglong]),
     "lcq_gemv_tc_plan_check": (_c.c_int, [_c.c_int] * 4 + [_c.POINTER(_c.c_int)]),
+    "lcq_gemv_tc_plan_cluster": (_c.c_int, [_c.c_int] * 4),
 }
 
 

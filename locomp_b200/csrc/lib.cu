@@ -434,6 +434,14 @@ int lcq_gemv_tc_plan_check(int M, int N, int K, int sm_count, int* fields) {
   return LCQ_OK;
 }
 
+int lcq_gemv_tc_plan_cluster(int M, int N, int K, int sm_count) {
+  if (!gemv_tc::supported(M, N, K, 32, LCQ_F16, LCQ_F16) || sm_count < 1) {
+    set_error("plan: problem not covered by GEMV_TC");
+    return LCQ_ERR_UNSUPPORTED;
+  }
+  return gemv_tc::make_plan(M, N, K, sm_count).p.cluster;
+}
+
 // ---------------------------------------------------------------- allocation-free decode entry
 // Scratch for lcq_matmul_int4_noalloc: lives in the library image, so every GPU that loads the
 // library holds these bytes until the process exits.  Zero at load time.

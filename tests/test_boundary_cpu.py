@@ -91,6 +91,22 @@ def test_gemv_plan_covers_every_tile_once(M):
                 assert f[0] <= max(2 * sms, f[2]) and f[6] <= 227 * 1024   # CTAs never wait on each other
 
 
+def test_small_problems_plan_into_clusters_and_large_ones_do_not():
+    lib = _lib.lib()
+    plan = lib.lcq_gemv_tc_plan_cluster
+    assert plan(1, 2048, 2048, 148) == 8          # 16 row blocks x 8 k tiles: one tile per CTA
+    assert plan(4, 8192, 2048, 148) == 4          # 64 row blocks: 4 CTAs each keep all 256 resident
+    assert plan(16, 2048, 8192, 148) == 8         # x per CTA is a share of K: no k ranges needed
+    assert plan(1, 49152, 2048, 148) == 1         # enough tiles per CTA: stream-K
+    assert plan(1, 128256, 8192, 148) == 1
+    assert plan(1, 192, 64, 148) == 1             # a single k tile cannot be shared
+    for M in (1, 3, 8, 16):                       # whatever the plan, a cluster never exceeds 8 CTAs
+        for N in (100, 1024, 5000, 16032):
+            for K in (64, 576, 2048, 28672):
+                c = plan(M, N, K, 148)
+                assert c in (1, 2, 4, 8), (M, N, K, c)
+
+
 def test_python_validation_happens_before_the_gpu():
     x = np.zeros(64, np.float32)
     with pytest.raises(ValueError, match="K=64"):
