@@ -1030,6 +1030,15 @@ inline bool cluster_mode_enabled() {
   return on;
 }
 
+// Largest cluster tried, per m-tile count: 8 with two CTAs per SM; 4 with one CTA per SM, where a
+// cluster of 8 needs 8 free SMs of one GPC at once and measured 1.5 - 1.8 x slower than clusters of 4.
+// (LCQ_GEMV_MAX_CLUSTER / LCQ_GEMV_MAX_CLUSTER2 override, read once.)
+inline int max_cluster_for(int MT) {
+  static const int v1 = [] { const char* e = getenv("LCQ_GEMV_MAX_CLUSTER"); const int n = e ? atoi(e) : 0; return (n == 1 || n == 2 || n == 4 || n == 8) ? n : 8; }();
+  static const int v2 = [] { const char* e = getenv("LCQ_GEMV_MAX_CLUSTER2"); const int n = e ? atoi(e) : 0; return (n == 1 || n == 2 || n == 4 || n == 8) ? n : 4; }();
+  return MT == 1 ? v1 : v2;
+}
+
 inline Plan make_plan(int M, int N, int K, int sm_count) {
   Plan pl;
   memset(&pl, 0, sizeof(pl));
@@ -1060,9 +1069,10 @@ inline Plan make_plan(int M, int N, int K, int sm_count) {
   const long long capacity = static_cast<long long>(sm_count) * ctas_per_sm;
   if (static_cast<long long>(p.n_rb) * p.nst < 4LL * capacity && cluster_mode_enabled()) {
     const int nst_cl = nstages_for(pl.MT, true);
-    int c = 8;
+    int c = max_cluster_for(pl.MT);
     while (c > 1) {
-      const bool resident = static_cast<long long>(p.n_rb) * c <= capacity;
+      // clusters of 8 do not pack the GPCs completely: leave a quarter of the CTA slots unused
+      const bool resident = static_cast<long long>(p.n_rb) * c <= (c == 8 ? capacity * 3 / 4 : capacity);
       const int xt = (p.nst + c - 1) / c;
       if (c <= p.nst && resident && smem_layout(nst_cl, pl.MPAD, pl.MT, xt, c).total <= max_dynamic_smem(ctas_per_sm)) break;
       c >>= 1;

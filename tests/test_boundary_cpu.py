@@ -96,7 +96,8 @@ def test_small_problems_plan_into_clusters_and_large_ones_do_not():
     plan = lib.lcq_gemv_tc_plan_cluster
     assert plan(1, 2048, 2048, 148) == 8          # 16 row blocks x 8 k tiles: one tile per CTA
     assert plan(4, 8192, 2048, 148) == 4          # 64 row blocks: 4 CTAs each keep all 256 resident
-    assert plan(16, 2048, 8192, 148) == 8         # x per CTA is a share of K: no k ranges needed
+    assert plan(16, 2048, 8192, 148) == 4         # x per CTA is a share of K: no k ranges needed; one CTA per SM: clusters of 4
+    assert plan(1, 4096, 4096, 148) == 4          # 32 row blocks x 8 would fill more than 3/4 of the CTA slots
     assert plan(1, 49152, 2048, 148) == 1         # enough tiles per CTA: stream-K
     assert plan(1, 128256, 8192, 148) == 1
     assert plan(1, 192, 64, 148) == 1             # a single k tile cannot be shared
