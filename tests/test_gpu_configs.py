@@ -224,3 +224,46 @@ def test_bf16_activation_range(scale, m):
     # scale-invariant form of the bar: 1e-2 relative plus 1e-2 of the output's RMS magnitude
     tol = 1e-2 * np.abs(ref) + 1e-2 * float(np.sqrt(np.mean(ref ** 2)))
     assert np.all(err <= tol), f"scale {scale}: max err {err.max():.4g}"
+
+
+_CLUSTER_CASE = r"""
+import sys
+import numpy as np, torch
+sys.path.insert(0, {root!r})
+import locomp_b200 as L
+from oracle import qmm_oracle as O
+outs = {{}}
+for (n, k, m) in ((2048, 2048, 1), (2048, 8192, 4), (1000, 2048, 8), (2048, 2048, 16), (640, 576, 3)):
+    rng = np.random.default_rng(n + k + m)
+    wp, s = O.make_w4(rng, n, k, 32, np.float16)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    y = L.quantized_matmul(torch.from_numpy(x).cuda(), torch.from_numpy(wp).cuda(), torch.from_numpy(s).cuda(), 32,
+                           out_dtype="f32", algo="gemv_tc")
+    outs[f"{{n}}_{{k}}_{{m}}"] = y.float().cpu().numpy()
+np.savez({path!r}, **outs)
+"""
+
+
+def test_cluster_mode_and_scratch_mode_agree(tmp_path):
+    """The small-problem plans with cluster mode on (partial sums meet in the cluster leader's shared
+    memory) and with LCQ_GEMV_CLUSTER=0 (whole row blocks per CTA, or global scratch) differ only in
+    how the float32 partial sums are associated: outputs agree to float32 round-off.  The switch is
+    read once per process, hence two child processes."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib = _lib.lib()
+    assert lib.lcq_gemv_tc_plan_cluster(1, 2048, 2048, 148) > 1      # the first case does run as clusters
+    results = []
+    for cluster in ("1", "0"):
+        path = str(tmp_path / f"cluster_{cluster}.npz")
+        env = dict(os.environ, LCQ_GEMV_CLUSTER=cluster)
+        out = subprocess.run([sys.executable, "-c", _CLUSTER_CASE.format(root=root, path=path)], capture_output=True,
+                             text=True, timeout=300, env=env, cwd=root)
+        assert out.returncode == 0, out.stderr[-800:]
+        results.append(np.load(path))
+    for key in results[0].files:
+        a, b = results[0][key], results[1][key]
+        scale = float(np.sqrt(np.mean(a.astype(np.float64) ** 2)))
+        assert np.abs(a - b).max() <= 2e-5 * scale, (key, float(np.abs(a - b).max()), scale)
