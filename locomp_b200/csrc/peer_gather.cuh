@@ -157,7 +157,15 @@ __global__ void __launch_bounds__(256) allgather_bulk_kernel(const PushArgs a) {
 
 // The pair form doubles the bytes on the wire and saves two fences (a few microseconds): it is used
 // while the extra bytes to all peers stay under 1 MiB.  Every rank takes the same decision.
-inline bool use_pairs(long long bytes_per_rank, int world) { return bytes_per_rank * (world - 1) <= (1LL << 20); }
+inline long long pair_limit_bytes() {     // LCQ_GATHER_PAIR_LIMIT_KIB overrides (read once)
+  static const long long v = [] {
+    const char* e = getenv("LCQ_GATHER_PAIR_LIMIT_KIB");
+    const long long n = e ? atoll(e) : 0;
+    return n > 0 ? n * 1024 : (1LL << 20);
+  }();
+  return v;
+}
+inline bool use_pairs(long long bytes_per_rank, int world) { return bytes_per_rank * (world - 1) <= pair_limit_bytes(); }
 
 inline int launch_push(const PushArgs& a, cudaStream_t stream) {
   const bool pairs = use_pairs(a.n16 * 16, a.world);
