@@ -72,27 +72,38 @@ __global__ void __launch_bounds__(256) allgather_push_kernel(const PushArgs a) {
     }
     a.data[a.rank][static_cast<long long>(a.rank) * a.n16 + i] = v;
   }
-  // receive: bounded polling on this rank's own staging area
+  // receive: bounded polling on this rank's own staging area.  For each of its elements a thread polls
+  // the pairs of ALL peers together (their loads are in flight at the same time), so a call costs about
+  // one round trip to L2 per retry, not one per peer.
   const uint64_t t0 = global_timer_ns();
   const uint64_t limit = wait_limit_ns();
   bool gave_up = false;
-  for (int r = 0; r < a.world && !gave_up; ++r) {
-    if (r == a.rank) continue;
-    const uint4* stage = a.data[a.rank] + static_cast<long long>(a.world) * a.n16 + (buf + r) * a.n16 * 2;
-    for (long long i = first; i < a.n16 && !gave_up; i += stride) {
-      uint4 lo, hi;
-      int spins = 0;
-      for (;;) {
-        lo = ld_volatile_v4(stage + 2 * i);
-        hi = ld_volatile_v4(stage + 2 * i + 1);
-        if (lo.y == seq && lo.w == seq && hi.y == seq && hi.w == seq) break;
-        if ((++spins & 63) == 0 && global_timer_ns() - t0 > limit) {
-          atomicExch(&g_device_status, 30 + r);
-          gave_up = true;
-          break;
+  const uint4* stage0 = a.data[a.rank] + static_cast<long long>(a.world) * a.n16 + buf * a.n16 * 2;
+  for (long long i = first; i < a.n16 && !gave_up; i += stride) {
+    unsigned pending = ((1u << a.world) - 1u) & ~(1u << a.rank);
+    int spins = 0;
+    while (pending != 0u) {
+      uint4 lo[MAX_RANKS], hi[MAX_RANKS];
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r) {
+        if ((pending >> r) & 1u) {
+          const uint4* stage = stage0 + static_cast<long long>(r) * a.n16 * 2;
+          lo[r] = ld_volatile_v4(stage + 2 * i);
+          hi[r] = ld_volatile_v4(stage + 2 * i + 1);
         }
       }
-      if (!gave_up) a.data[a.rank][static_cast<long long>(r) * a.n16 + i] = make_uint4(lo.x, lo.z, hi.x, hi.z);
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r) {
+        if (((pending >> r) & 1u) && lo[r].y == seq && lo[r].w == seq && hi[r].y == seq && hi[r].w == seq) {
+          a.data[a.rank][static_cast<long long>(r) * a.n16 + i] = make_uint4(lo[r].x, lo[r].z, hi[r].x, hi[r].z);
+          pending &= ~(1u << r);
+        }
+      }
+      if (pending != 0u && (++spins & 63) == 0 && global_timer_ns() - t0 > limit) {
+        atomicExch(&g_device_status, 30 + (__ffs(pending) - 1));
+        gave_up = true;
+        break;
+      }
     }
   }
   // the last CTA to finish advances the sequence number (every CTA has read it by then)
