@@ -59,6 +59,7 @@ def graph_us(ctx: Ctx, launchers, min_launches: int = 200, replays: int = 3, per
     st = ctx.stream
     n = len(launchers)
     reps = max(1, -(-min_launches // n))
+    torch.cuda.synchronize()                      # inputs were made on the default stream; `st` does not wait for it
     with torch.cuda.stream(st):
         for f in launchers:                       # eager warm-up: sets kernel attributes before capture
             f(st.cuda_stream)
