@@ -372,3 +372,38 @@ def test_int8_tma_kernel_matches_oracle_and_simt(n, k, g, m, xdt):
         assert y16.dtype == torch.float16
         _check16(y16.float().cpu().numpy(), O.matmul_int8(x.astype(np.float32), w8, s8.astype(np.float16), g))
     _device_status_ok()
+
+
+def test_c_abi_sharding_context_with_one_rank():
+    """lcq_shard_ctx_* at world = 1 (the two-rank form runs in tests/sharded_worker.py): create,
+    no handles to exchange, two consecutive calls (the two regions alternate), destroy."""
+    import ctypes
+    lib = _lib.lib()
+    n, k = 384 + 32, 2048
+    rng = np.random.default_rng(11)
+    wp, s = O.make_w4(rng, n, k, 32, np.float16)
+    wd, sd = torch.from_numpy(wp).cuda(), torch.from_numpy(s).cuda()
+    ctx = ctypes.c_void_p()
+    handles = ctypes.create_string_buffer(128)
+    _lib.check(lib.lcq_shard_ctx_create(0, 1, 16 * n * 2, ctypes.byref(ctx), handles))
+    try:
+        torch.cuda.synchronize()
+        for m in (1, 16):
+            x = rng.standard_normal((m, k)).astype(np.float16)
+            xd = torch.from_numpy(x).cuda()
+            out_ptr = ctypes.c_void_p()
+            _lib.check(lib.lcq_sharded_matmul_int4(ctx, xd.data_ptr(), wd.data_ptr(), sd.data_ptr(), ctypes.byref(out_ptr),
+                                                   m, n, k, 32, _lib.F16, _lib.F16, _lib.F16, _lib.ALGO_AUTO, None))
+            torch.cuda.synchronize()
+
+            class _Mem:
+                __cuda_array_interface__ = {"shape": (m * n,), "typestr": "<f2", "data": (out_ptr.value, False), "version": 3}
+            got = torch.as_tensor(_Mem(), device="cuda").cpu().numpy().reshape(m, n).astype(np.float32)
+            ref = O.matmul_int4(x.astype(np.float32), wp, s, 32)
+            assert np.all(np.abs(got - ref) <= 1e-2 + 1e-2 * np.abs(ref)), float(np.abs(got - ref).max())
+        assert lib.lcq_check_device_status(None) == 0
+        bad = ctypes.c_void_p()
+        assert lib.lcq_sharded_matmul_int4(ctx, xd.data_ptr(), wd.data_ptr(), sd.data_ptr(), ctypes.byref(bad), 32, n, k, 32,
+                                           _lib.F16, _lib.F16, _lib.F16, _lib.ALGO_AUTO, None) == _lib.ERR_BAD_ARG   # slice over the limit
+    finally:
+        _lib.check(lib.lcq_shard_ctx_destroy(ctx))
