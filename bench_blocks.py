@@ -143,7 +143,7 @@ class Problem:
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures summarised under
 # profiles/, valid only for the kernel source they were taken from: {source hash: {(K, N, M): bytes}}
 TRAFFIC_NCU = {
-    "9e9244ba4a1c": {(2048, 49152, 1): 56_685_000, (2048, 49152, 16): 56_810_000, (2048, 8192, 1): 9_469_800},
+    "011311b5b0e9": {(2048, 49152, 1): 56_690_000, (2048, 49152, 16): 56_810_000, (2048, 8192, 1): 9_469_952},
 }
 
 

@@ -362,36 +362,17 @@ __device__ __forceinline__ void store_row_group(const Params& p, const float (&y
   else store_row_group_t<float, MT, NC>(static_cast<float*>(p.out), p, y, n0, t4);
 }
 
-// Settles the 32 rows of one row group at the end of a CTA's share of a row block (called by the
-// row group's slice-0 warp with the slices already added up in y).  `whole`: the CTA produced the
-// entire row block, so the values are the outputs.  Otherwise the row block has several
-// contributors (other CTAs of this k-range and / or other k-ranges): publish the partial, count,
-// and let the last contributor sum all partials in slot order.  `seen_lane0` is the counter value
+// Settles the 32 rows of one row group of a row block that has several contributors (other CTAs of
+// this k-range and / or other k-ranges); called by the row group's slice-0 warp with the slices
+// already added up in y: publish the partial, count, and let the last contributor sum all partials
+// in slot order -- or, if the counter shows that everybody else has already published, add their
+// partials to the values still in registers and write the output without publishing.  `seen_lane0` is the counter value
 // lane 0 read (with an acquire load) a tile earlier.  Inline on purpose: an out-of-line call parks
 // the caller's registers on the stack, and with nearly all of L1 carved out as shared memory that
 // round trip goes to L2 (about a microsecond per call, measured).
 template <int MT, int NC>
 __device__ __forceinline__ void flush_row_group(const Params& p, const float (&y)[2][MT][4], int rb, int rg, int g, int t4,
-                                             int lane, bool whole, int seen_lane0, const CtaInfo* info) {
-  const int n0 = rb * ROWS + rg * 32 + g;               // rows n0 + 16*sl and n0 + 16*sl + 8
-  if (whole) {
-#pragma unroll
-    for (int sl = 0; sl < 2; ++sl) {
-      const int nA = n0 + 16 * sl, nB = nA + 8;
-#pragma unroll
-      for (int jm = 0; jm < MT; ++jm) {
-#pragma unroll
-        for (int e = 0; e < NC; ++e) {
-          const int m = 8 * jm + 2 * t4 + e;
-          if (m < p.M) {
-            if (nA < p.N) store_out(p.out, p.out_dtype, static_cast<long long>(m) * p.N + nA, y[sl][jm][e]);
-            if (nB < p.N) store_out(p.out, p.out_dtype, static_cast<long long>(m) * p.N + nB, y[sl][jm][2 + e]);
-          }
-        }
-      }
-    }
-    return;
-  }
+                                             int lane, int seen_lane0, const CtaInfo* info) {
   Sched sch;
   sch.S_kr = info->S_kr; sch.T = info->T; sch.G = info->G;
   const int kr = info->kr, j = info->j;
@@ -472,21 +453,14 @@ __device__ __forceinline__ void flush_row_group(const Params& p, const float (&y
               sum[sl][jm][e][1] += mine[u] ? y[sl][jm][2 + e] : v[u][sl][jm][e][1];
             }
     }
+    float out_y[2][MT][4];
 #pragma unroll
-    for (int sl = 0; sl < 2; ++sl) {
-      const int nA = n0 + 16 * sl, nB = nA + 8;
+    for (int sl = 0; sl < 2; ++sl)
 #pragma unroll
-      for (int jm = 0; jm < MT; ++jm) {
+      for (int jm = 0; jm < MT; ++jm)
 #pragma unroll
-        for (int e = 0; e < NC; ++e) {
-          const int m = 8 * jm + 2 * t4 + e;
-          if (m < p.M) {
-            if (nA < p.N) store_out(p.out, p.out_dtype, static_cast<long long>(m) * p.N + nA, sum[sl][jm][e][0]);
-            if (nB < p.N) store_out(p.out, p.out_dtype, static_cast<long long>(m) * p.N + nB, sum[sl][jm][e][1]);
-          }
-        }
-      }
-    }
+        for (int e = 0; e < NC; ++e) { out_y[sl][jm][e] = sum[sl][jm][e][0]; out_y[sl][jm][2 + e] = sum[sl][jm][e][1]; }
+    store_row_group<MT, NC>(p, out_y, rb, rg, g, t4);
     __syncwarp();
     if (lane == 0) *counter = 0;
     return;
@@ -982,7 +956,7 @@ w4a16_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
             }
           } else {
             if (whole) store_row_group<MT, NC>(p, y, rb, rg, g, t4);
-            else flush_row_group<MT, NC>(p, y, rb, rg, g, t4, lane, false, seen, info);
+            else flush_row_group<MT, NC>(p, y, rb, rg, g, t4, lane, seen, info);
           }
         }
       }
