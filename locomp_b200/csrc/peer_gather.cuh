@@ -137,12 +137,24 @@ __global__ void __launch_bounds__(256) allgather_bulk_kernel(const PushArgs a) {
   griddep_launch_dependents();
   griddep_wait();                // src is the output of the kernel before us on the stream
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < a.n16; i += stride) {
-    const uint4 v = a.src[i];
-    const long long o = static_cast<long long>(a.rank) * a.n16 + i;
+  // four 16-byte pieces per thread and step: all four loads in flight before the first peer store
+  for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < a.n16; i0 += 4 * stride) {
+    uint4 v[4];
 #pragma unroll
-    for (int g = 0; g < MAX_RANKS; ++g)
-      if (g < a.world) a.data[g][o] = v;
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * stride;
+      v[u] = i < a.n16 ? a.src[i] : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < a.n16) {
+        const long long o = static_cast<long long>(a.rank) * a.n16 + i;
+#pragma unroll
+        for (int g = 0; g < MAX_RANKS; ++g)
+          if (g < a.world) a.data[g][o] = v[u];
+      }
+    }
   }
   __syncthreads();
   if (threadIdx.x != 0) return;
@@ -180,8 +192,9 @@ inline bool use_pairs(long long bytes_per_rank, int world) { return bytes_per_ra
 
 inline int launch_push(const PushArgs& a, cudaStream_t stream) {
   const bool pairs = use_pairs(a.n16 * 16, a.world);
+  static const int bulk_cap = [] { const char* e = getenv("LCQ_GATHER_BULK_CTAS"); const int n = e ? atoi(e) : 0; return n > 0 ? n : 148; }();
   long long blocks = (a.n16 + 255) / 256;
-  if (blocks > (pairs ? 64 : 32)) blocks = pairs ? 64 : 32;
+  if (blocks > (pairs ? 64 : bulk_cap)) blocks = pairs ? 64 : bulk_cap;
   if (blocks < 1) blocks = 1;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
